@@ -1,0 +1,254 @@
+/*
+ * ps_b200.h — C ABI of the B200 (sm_100a) chunk optimizer step.
+ *
+ * The library replaces the native half of PatrickStar's mixed-precision
+ * optimizer step: the pybind module `cpu_adam_op` (create_adam / adam_update /
+ * destroy_adam, patrickstar/ops/csrc/adam/cpu_adam.cpp:751-756) and the
+ * per-chunk work that patrickstar/ops/fp16_cpu_adam.py and
+ * patrickstar/ops/chunk_io_buff.py wrap around it (fp16 grad chunk read,
+ * fp32 -> fp16 param chunk write-back, overflow gate, loss-scale update).
+ *
+ * Conventions
+ *   - plain C: pointers, sizes, scalars.  No torch, no C++ types.
+ *   - every pointer named *_dev is a device address (cudaMalloc'ed or pinned
+ *     host memory mapped into the device address space); the library never
+ *     allocates or frees device memory behind these calls.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *     stream.  All device work is enqueued on it and nothing synchronises
+ *     unless the comment of a function says so.
+ *   - return value: 0 on success, a negative PS_ERR_* code otherwise.  Nothing
+ *     throws, traps or aborts.  (The reference always returns 0, ignores CUDA
+ *     return codes and dereferences a null pointer on an unknown optimizer id,
+ *     cpu_adam.cpp:721-722; here those cases are reported.)
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point returns PS_ERR_CUDA.
+ */
+#ifndef PS_B200_H
+#define PS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PS_OK 0
+#define PS_ERR_INVALID (-1)    /* null pointer, bad size, bad hyper-parameter */
+#define PS_ERR_UNKNOWN_ID (-2) /* optimizer id was never created / already destroyed */
+#define PS_ERR_ALIGN (-3)      /* a pointer or offset breaks the stated alignment rule */
+#define PS_ERR_CUDA (-4)       /* a CUDA runtime call failed; see ps_last_cuda_error() */
+#define PS_ERR_TABLE (-5)      /* chunk / segment table failed validation */
+#define PS_ERR_LIMIT (-6)      /* a stated maximum (groups, slots, static capacity) exceeded */
+
+#define PS_MAX_GROUPS 15              /* hyper-parameter groups per optimizer */
+#define PS_MAX_SLOTS (PS_MAX_GROUPS + 1) /* slot 0 = first call of a step, 1+g = later calls of group g */
+
+/* One local chunk.  Mirrors what the reference keeps per chunk id: the fp16
+ * param chunk whose storage the gradients reuse (patrickstar/core/hook.py:214-216)
+ * and the fp32 master / momentum / variance chunks laid out like it
+ * (patrickstar/ops/fp16_cpu_adam.py:132-170).  All four base pointers must be
+ * 16-byte aligned.  Elements outside every segment are left untouched. */
+typedef struct ps_chunk_desc {
+    float* p32;        /* fp32 master params, updated in place                  */
+    float* exp_avg;    /* fp32 momentum, updated in place                       */
+    float* exp_avg_sq; /* fp32 variance, updated in place                       */
+    uint16_t* h16;     /* fp16 slot: gradients on entry, updated params on exit */
+    uint32_t numel;    /* elements in use (<= chunk capacity)                   */
+    uint32_t seg_begin; /* [seg_begin, seg_end) in the segment table            */
+    uint32_t seg_end;
+    uint32_t reserved;
+} ps_chunk_desc;
+
+/* A run of elements of one chunk that shares hyper-parameters: [start, end)
+ * in chunk-local element offsets, sorted and non-overlapping within a chunk.
+ * `slot` selects the ps_hyper_slot the step-begin kernel prepared. */
+typedef struct ps_segment {
+    uint32_t start;
+    uint32_t end;
+    uint32_t slot;
+    uint32_t reserved;
+} ps_segment;
+
+/* Hyper-parameters of one param group, as FP16Adam keeps them per parameter
+ * (patrickstar/ops/fp16_cpu_adam.py:112-120). */
+typedef struct ps_group_hyper {
+    float lr, beta1, beta2, eps, weight_decay;
+    int32_t adamw_mode;
+    int32_t reserved[2];
+} ps_group_hyper;
+
+/* What one step needs besides the tables.  `first_group` is the group of the
+ * first segment the rank visits in a step and `last_group` that of the last
+ * one; `n_calls` is the number of segments (the reference makes one
+ * adam_update call per tensor, and its beta^t depends on that call history,
+ * patrickstar/ops/csrc/includes/cpu_adam.h:143-162). */
+typedef struct ps_step_plan {
+    double clip;         /* gradient_clipping of FP16Adam; <= 0 disables (fp16_cpu_adam.py:365-379) */
+    ps_group_hyper groups[PS_MAX_GROUPS];
+    int32_t n_groups;
+    int32_t first_group;
+    int32_t last_group;
+    int32_t n_calls;
+    float grad_divisor;  /* world size when the fp16 `payload /= world_size` of
+                            patrickstar/core/client.py:838 is folded into the load; <= 1 disables */
+    int32_t bias_correction;
+} ps_step_plan;
+
+/* Device-resident loss-scaler state: the fields of DynamicLossScaler
+ * (patrickstar/fp16/loss_scaler.py:107-124) with Python's float as double and
+ * Python's int as int64.  dynamic == 0 is the static LossScaler (:46-76),
+ * dynamic < 0 means "no loss scaler" (loss_scale -1 in ds_cpu_adam_update). */
+typedef struct ps_scaler_state {
+    double cur_scale;
+    double scale_factor;
+    double min_scale;
+    int64_t cur_iter;
+    int64_t last_overflow_iter;
+    int64_t scale_window;
+    int32_t delayed_shift;
+    int32_t cur_hysteresis;
+    int32_t consecutive_hysteresis;
+    int32_t dynamic;
+} ps_scaler_state;
+
+/* Derived per-slot constants, prepared on the device by ps_step_begin exactly
+ * as Adam_Optimizer::Step derives them (cpu_adam.cpp:42-46). */
+typedef struct ps_hyper_slot {
+    float loss_scale; /* <= 0: no unscale */
+    float beta1, beta2, beta1_minus1, beta2_minus1;
+    float bias2_sqrt, eps, step_size;
+    float weight_decay, w_decay;
+    float clip;         /* already min(65504, clip * scale); <= 0 disabled */
+    float grad_divisor; /* <= 1 disabled */
+    int32_t adamw_mode;
+    int32_t reserved[3];
+} ps_hyper_slot;
+
+/* Device-resident control block of one optimizer (one per FP16Adam object). */
+typedef struct ps_step_ctrl {
+    int32_t skip;          /* set by ps_step_begin: 1 = this step is skipped */
+    int32_t error;         /* sticky device-side error word (0 = none)       */
+    uint64_t step;         /* state["step"]: counts non-skipped steps        */
+    uint64_t n_skipped;    /* total skipped steps                            */
+    /* emulation of Adam_Optimizer's call-history state (cpu_adam.h:143-162) */
+    uint64_t native_step;
+    float betta1, betta2, betta1_t, betta2_t;
+    ps_hyper_slot slots[PS_MAX_SLOTS];
+} ps_step_ctrl;
+
+/* ------------------------------------------------------------------ */
+/* library                                                              */
+/* ------------------------------------------------------------------ */
+int ps_version(void);
+const char* ps_strerror(int code);
+int ps_last_cuda_error(void); /* cudaError_t of the last failed runtime call on this thread */
+
+/* ------------------------------------------------------------------ */
+/* tensor-level API: 1:1 image of the cpu_adam_op module                */
+/* ------------------------------------------------------------------ */
+
+/* create_adam (cpu_adam.cpp:379-417).  Host-only. */
+int ps_adam_create(int optimizer_id, float alpha, float betta1, float betta2, float eps,
+                   float weight_decay, int adamw_mode, int should_log);
+
+/* destroy_adam (cpu_adam.cpp:744-749).  Host-only. */
+int ps_adam_destroy(int optimizer_id);
+
+/* adam_update / ds_adam_step (cpu_adam.cpp:700-742) on device pointers.
+ * params/exp_avg/exp_avg_sq: fp32 [n], updated in place.  grads: fp16 bits
+ * (g_is_half != 0) or fp32, read-only.  loss_scale <= 0: no unscale.
+ * p16_out (may be NULL): receives half(params) — the write-back the reference
+ * does as a separate chunk copy (patrickstar/ops/chunk_io_buff.py:85-128); it
+ * may alias `grads`.  Pointers need only their natural alignment; when the
+ * four of them are not mutually 16-byte co-aligned a slower element-wise
+ * kernel is used. */
+int ps_adam_update(int optimizer_id, size_t step, float lr, float beta1, float beta2, float epsilon,
+                   float weight_decay, int bias_correction, float* params_dev, const void* grads_dev,
+                   float* exp_avg_dev, float* exp_avg_sq_dev, size_t n, int g_is_half,
+                   float loss_scale, uint16_t* p16_out_dev, void* stream);
+
+/* Host-only: beta1^t, beta2^t, bias_correction1, bias_correction2 and the step
+ * the optimizer object holds after its last ps_adam_update (for tests). */
+int ps_adam_get_state(int optimizer_id, float out[4], uint64_t* step);
+
+/* ------------------------------------------------------------------ */
+/* chunk-level API: what FP16Adam.step drives                           */
+/* ------------------------------------------------------------------ */
+
+/* Host-side validation of a chunk table and its segment table before they are
+ * uploaded: 16-byte aligned non-null bases, numel <= chunk_capacity, segments
+ * sorted, non-overlapping, inside numel, slot < n_slots. */
+int ps_table_check(const ps_chunk_desc* chunks_host, uint32_t n_chunks, const ps_segment* segs_host,
+                   uint32_t n_segs, uint32_t n_slots, uint32_t chunk_capacity);
+
+/* Host-only helper: out[2*i] = float(pow(double(beta1), t0+i)), out[2*i+1] the
+ * same for beta2 — the values IncrementStep's pow branch produces
+ * (cpu_adam.h:147-156).  The step-begin kernel looks them up by the
+ * device-resident step counter. */
+int ps_pow_table_fill(float beta1, float beta2, uint64_t t0, uint64_t count, float* out_host);
+
+/* Initialise a control block on the device (step counter, beta history).
+ * Enqueues one small kernel. */
+int ps_ctrl_init(ps_step_ctrl* ctrl_dev, uint64_t step, float betta1, float betta2, void* stream);
+
+/* Initialise a scaler state on the device from a host copy. */
+int ps_scaler_init(ps_scaler_state* scaler_dev, const ps_scaler_state* init_host, void* stream);
+
+/* Overflow scan — DynamicLossScaler._has_inf_or_nan (loss_scaler.py:133-155)
+ * over the fp16 slot of every chunk of the table; ORs 1 into *flag_dev when an
+ * inf or nan is found.  Read-only, 2 B/element. */
+int ps_overflow_scan(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                     int32_t* flag_dev, void* stream);
+
+/* Same test on one plain fp16 buffer (FP16Adam.check_overflow on one grad). */
+int ps_overflow_scan_buffer(const uint16_t* g_dev, size_t n, int32_t* flag_dev, void* stream);
+
+/* Head of FP16Adam.step (fp16_cpu_adam.py:549-606, 624-625) as one
+ * single-thread kernel, no host sync: reads *flag_dev (already MAX-reduced
+ * over ranks); on overflow sets ctrl->skip, otherwise increments the step
+ * counter, replays IncrementStep/update_state for the plan's calls using
+ * pow_table_dev (pairs as written by ps_pow_table_fill for each group g at
+ * pow_table_dev + 2*(g*pow_table_len + t)) and fills the hyper slots with the
+ * scale in force for this step.  Then applies DynamicLossScaler.update_scale
+ * (loss_scaler.py:158-182) and clears the flag. */
+int ps_step_begin(ps_step_ctrl* ctrl_dev, ps_scaler_state* scaler_dev, int32_t* flag_dev,
+                  const ps_step_plan* plan_host, const float* pow_table_dev, uint64_t pow_table_len,
+                  void* stream);
+
+/* DynamicLossScaler.update_scale (loss_scaler.py:158-182) alone, for callers that
+ * drive the scaler themselves: overflow is *flag_dev != 0 when flag_dev is not
+ * NULL (the flag is cleared afterwards), else `overflow_host`. */
+int ps_scaler_update(ps_scaler_state* scaler_dev, int32_t* flag_dev, int overflow_host, void* stream);
+
+/* The fused chunk step over a table of chunks, one launch.  When ctrl->skip is
+ * 0: per element unscale the fp16 grad, Adam/AdamW on fp32 master, m, v in the
+ * reference's operation order (cpu_adam.cpp:33-144), write half(master) into
+ * the fp16 slot (28 B/element).  When ctrl->skip is 1: restore the fp16 slot
+ * from the fp32 master (fp16_cpu_adam.py:298-309; 6 B/element). */
+int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                  const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, void* stream);
+
+/* Copies the device scaler state / control block to the host.  Synchronises
+ * `stream`.  (DynamicLossScaler.loss_scale, state["step"].) */
+int ps_scaler_read(const ps_scaler_state* scaler_dev, ps_scaler_state* out_host, void* stream);
+int ps_ctrl_read(const ps_step_ctrl* ctrl_dev, ps_step_ctrl* out_host, void* stream);
+
+/* scaled = loss * cur_scale on the device (DynamicLossScaler.backward,
+ * loss_scaler.py:188-190) without reading the scale back: fp32 in/out, n values. */
+int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scaler_state* scaler_dev,
+                  void* stream);
+
+/* Tuning knobs for measurements: "unroll" (1, 2, 4: 128-bit groups per thread
+ * per tile of the step kernels), "scan_unroll" (1, 2, 4), "blocks_per_sm"
+ * (0 = occupancy calculator).  No counterpart in the reference. */
+int ps_tune(const char* key, int value);
+
+/* Kernel launch counter: number of kernels this library has launched in this
+ * process (for benchmark bookkeeping). */
+uint64_t ps_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PS_B200_H */

@@ -1,0 +1,87 @@
+"""TEST INFRASTRUCTURE — the protocol of ``FP16Adam.step`` on the CPU.
+
+Restates patrickstar/ops/fp16_cpu_adam.py:472-628 over the C Adam oracle for
+one rank's local chunks:
+
+  * overflow gate (``:287-310``): if any local gradient holds inf/nan (the flag
+    is the OR over ranks), every local fp16 chunk is restored from the fp32
+    master, the scaler takes ``update_scale(True)`` and the step counter is NOT
+    advanced (``:549-558``);
+  * otherwise ``state["step"] += 1`` (``:574``), one ``adam_update`` call per
+    tensor piece in storage order (``:336-428``) on ONE optimizer object — so
+    the reference's call-history dependent beta^t is reproduced — then the fp16
+    chunk := cast(fp32 master) (``chunk_io_buff.py:85-128``) and
+    ``update_scale(False)`` (``:624-625``);
+  * the gradient is first divided by the world size in fp16
+    (patrickstar/core/client.py:838) when ``world_size > 1`` and clamped in
+    fp16 when gradient clipping is on (``:365-379``, GPU flavour).
+
+Arrays are numpy: fp16 chunks as uint16/float16, states as float32.
+"""
+import numpy as np
+
+from . import port
+
+
+class StepOracle:
+    def __init__(self, calls, groups, scaler, use_adamw, gradient_clipping=-1, world_size=1):
+        """calls: list of (chunk_index, start, end, group) in visiting order.
+        groups: list of dicts lr / betas / eps / weight_decay."""
+        self.calls = list(calls)
+        self.groups = groups
+        self.scaler = scaler
+        self.use_adamw = use_adamw
+        self.clip = gradient_clipping
+        self.world_size = world_size
+        g0 = groups[0]
+        # create_adam with the constructor's hyper-parameters (fp16_cpu_adam.py:183-193)
+        self.adam = port.OracleAdam(g0["lr"], g0["betas"][0], g0["betas"][1], g0["eps"],
+                                    g0["weight_decay"], use_adamw)
+        self.step_count = 0
+        self.skipped = 0
+
+    def _prepared_grad(self, g16):
+        g = g16.copy()
+        if self.world_size > 1:
+            port.div_world_f16(g.view(np.uint16), self.world_size)
+        if self.clip > 0:
+            c = self.clip
+            if self.scaler is not None:
+                c = c * self.scaler.loss_scale
+            c = np.float32(min(65504.0, c))
+            g = np.clip(g.astype(np.float32), -c, c).astype(np.float16)
+        return g
+
+    def step(self, h16, p32, exp_avg, exp_avg_sq, overflow=None):
+        """h16 / p32 / exp_avg / exp_avg_sq: lists of per-chunk arrays (in place).
+        overflow: the flag after the all-reduce; None = derive from h16."""
+        dynamic = self.scaler is not None and getattr(self.scaler, "dynamic", False)
+        if overflow is None:
+            overflow = dynamic and any(port.has_inf_or_nan_f16(h.view(np.uint16)) for h in h16)
+        if not dynamic:
+            overflow = False
+        if overflow:
+            for h, p in zip(h16, p32):
+                port.cast_fp32_to_fp16(p, h.view(np.uint16))
+            self.scaler.update_scale(True)
+            self.skipped += 1
+            return True
+        self.step_count += 1
+        loss_scale = self.scaler.loss_scale if self.scaler is not None else -1
+        for (c, s, e, g) in self.calls:
+            hp = self.groups[g]
+            grad = self._prepared_grad(h16[c][s:e].view(np.float16))
+            p = np.ascontiguousarray(p32[c][s:e])
+            m = np.ascontiguousarray(exp_avg[c][s:e])
+            v = np.ascontiguousarray(exp_avg_sq[c][s:e])
+            self.adam.adam_update(self.step_count, hp["lr"], hp["betas"][0], hp["betas"][1], hp["eps"],
+                                  hp["weight_decay"], True, p, grad, m, v, loss_scale)
+            p32[c][s:e] = p
+            exp_avg[c][s:e] = m
+            exp_avg_sq[c][s:e] = v
+            out = np.empty(e - s, dtype=np.uint16)
+            port.cast_fp32_to_fp16(p, out)
+            h16[c].view(np.uint16)[s:e] = out
+        if self.scaler is not None:
+            self.scaler.update_scale(False)
+        return False

@@ -1,0 +1,195 @@
+"""Chunk manager for the optimizer step.
+
+The slice of ``PatrickStarClient`` (patrickstar/core/client.py) the optimizer
+step touches: it owns the chunk payloads, hands out tensor views into them
+(``access_data``), says which chunks are local, and runs the two chunk
+collectives of a communication group (reduce-scatter of fp16 grads
+client.py:818-856, all-gather of fp16 params client.py:428-497).
+
+Memory layout on one GPU
+  * ``fp16`` — ONE contiguous fp16 buffer of ``n_chunks * chunk_size`` elements
+    holding every chunk of the list, local and remote, in chunk order.  Chunk k
+    of communication group g is slice ``k % world`` of the group's contiguous
+    ``world * chunk_size`` run, so reduce-scatter and all-gather run in place
+    on it with no flatten copy.  Parameters are views into this buffer; their
+    storage receives the gradients after backward
+    (patrickstar/core/hook.py:214-216) and the updated fp16 params after the
+    step.
+  * ``p32`` / ``exp_avg`` / ``exp_avg_sq`` — fp32 master, momentum, variance of
+    the LOCAL chunks only (patrickstar/ops/fp16_cpu_adam.py:132-170), laid out
+    like the fp16 chunk.  The first ``n_resident`` local chunks live in HBM;
+    the rest ("hybrid" placement, fp16_cpu_adam.py:523-528) live in pinned host
+    memory and are streamed through staging slots by the offload pipeline.
+"""
+import torch
+
+from . import comm
+from .chunk_list import ChunkLayout, DEFAULT_CHUNK_SIZE
+
+
+class ChunkClient:
+    def __init__(self, rank=0, default_chunk_size=DEFAULT_CHUNK_SIZE, config=None, world_size=None,
+                 device=None, pack="no_split", process_group=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("patrickstar_b200 needs a CUDA device (sm_100a); none found")
+        self.local_rank = rank
+        if world_size is None:
+            world_size = (torch.distributed.get_world_size(process_group)
+                          if torch.distributed.is_available() and torch.distributed.is_initialized() else 1)
+        self.world_size = world_size
+        self.rank = (torch.distributed.get_rank(process_group)
+                     if world_size > 1 and torch.distributed.is_initialized() else 0)
+        self.process_group = process_group
+        self.device = torch.device("cuda", rank) if device is None else torch.device(device)
+        self.config = config or {}
+        self.layout = ChunkLayout(default_chunk_size, world_size, pack)
+        self.default_chunk_size = default_chunk_size
+        self.params = {}      # name -> fp16 nn.Parameter view
+        self.fp16 = None
+        self.p32 = self.exp_avg = self.exp_avg_sq = None          # device-resident local chunks
+        self.p32_host = self.exp_avg_host = self.exp_avg_sq_host = None  # offloaded local chunks
+        self.n_resident = 0
+        self.local_ids = []
+
+    # ------------------------------------------------------------- registration
+    def append_tensor_list(self, specs, shapes=None):
+        return self.layout.append_tensor_list(specs, shapes)
+
+    def register_module(self, module, group_of=None):
+        """Register every parameter of an nn.Module, one atomic list per
+        sub-module as the reference's pre-process context does
+        (patrickstar/core/preprocess.py:341-435).  ``group_of(name, param)``
+        gives the hyper-parameter group index (default 0)."""
+        self._pending = []
+        for mod_name, mod in module.named_modules():
+            specs, shapes, plist = [], [], []
+            for pname, p in mod.named_parameters(recurse=False):
+                full = (mod_name + "." if mod_name else "") + pname
+                g = group_of(full, p) if group_of else 0
+                specs.append((full, p.numel(), g))
+                shapes.append(tuple(p.shape))
+                plist.append((full, p))
+            if specs:
+                self.layout.append_tensor_list(specs, shapes)
+                self._pending.extend(plist)
+        return self
+
+    # ---------------------------------------------------------------- allocation
+    def allocate(self, state_budget_bytes=None, init_master_from_fp16=True):
+        """Freeze the layout and allocate the payloads.  ``state_budget_bytes``
+        caps the HBM spent on fp32 master/momentum/variance chunks; local chunks
+        beyond it are placed in pinned host memory (hybrid placement)."""
+        lay = self.layout.freeze()
+        cs = lay.chunk_size
+        self.local_ids = lay.local_chunk_ids(self.rank)
+        n_local = len(self.local_ids)
+        per_chunk = 3 * 4 * cs
+        if state_budget_bytes is None:
+            self.n_resident = n_local
+        else:
+            self.n_resident = max(0, min(n_local, int(state_budget_bytes) // per_chunk))
+        n_off = n_local - self.n_resident
+        dev = self.device
+        self.fp16 = torch.zeros(lay.n_chunks * cs, dtype=torch.float16, device=dev)
+
+        def dev_buf():
+            return torch.zeros(max(self.n_resident, 0) * cs, dtype=torch.float32, device=dev)
+
+        def host_buf():
+            return torch.zeros(n_off * cs, dtype=torch.float32).pin_memory() if n_off else None
+
+        self.p32, self.exp_avg, self.exp_avg_sq = dev_buf(), dev_buf(), dev_buf()
+        self.p32_host, self.exp_avg_host, self.exp_avg_sq_host = host_buf(), host_buf(), host_buf()
+        # parameters registered from a module: move their values into the chunks
+        for full, p in getattr(self, "_pending", []):
+            info = lay.tensor(full)
+            view = self.fp16_view(info)
+            view.copy_(p.detach().to(device=dev, dtype=torch.float16).reshape(-1))
+            p.data = view.view(p.shape)
+            self.params[full] = p
+        if not getattr(self, "_pending", None):
+            # tensors registered by shape only: parameters are views of the fp16 buffer
+            for info in lay.tensors:
+                view = self.fp16_view(info).view(info.shape)
+                self.params[info.name] = torch.nn.Parameter(view, requires_grad=False)
+        if init_master_from_fp16 and getattr(self, "_pending", None):
+            for k, c in enumerate(self.local_ids):
+                self.chunk_state(k)[0].copy_(self.fp16_chunk(c).float())
+        self._pending = []
+        return self
+
+    # -------------------------------------------------------------------- views
+    def fp16_chunk(self, chunk_id):
+        cs = self.layout.chunk_size
+        return self.fp16[chunk_id * cs:(chunk_id + 1) * cs]
+
+    def fp16_group(self, group_id):
+        n = self.layout.chunk_size * self.world_size
+        return self.fp16[group_id * n:(group_id + 1) * n]
+
+    def fp16_view(self, info):
+        s = info.flat_start(self.layout.chunk_size)
+        return self.fp16[s:s + info.numel]
+
+    def chunk_state(self, local_index):
+        """(p32, exp_avg, exp_avg_sq) chunk views of the local_index-th local chunk;
+        device tensors for resident chunks, pinned host tensors for offloaded ones."""
+        cs = self.layout.chunk_size
+        if local_index < self.n_resident:
+            sl = slice(local_index * cs, (local_index + 1) * cs)
+            return self.p32[sl], self.exp_avg[sl], self.exp_avg_sq[sl]
+        k = local_index - self.n_resident
+        sl = slice(k * cs, (k + 1) * cs)
+        return self.p32_host[sl], self.exp_avg_host[sl], self.exp_avg_sq_host[sl]
+
+    def is_local(self, name):
+        """True when every element of the tensor lies in chunks this rank owns."""
+        info = self.layout.tensor(name)
+        cs = self.layout.chunk_size
+        first = info.chunk_id
+        last = (info.flat_start(cs) + max(info.numel, 1) - 1) // cs
+        return all(self.layout.is_local(c, self.rank) for c in range(first, last + 1))
+
+    def access_data(self, name, kind="p32"):
+        """Views of one tensor's optimizer state, one per chunk piece:
+        list of (tensor_view, flat_offset_in_tensor).  ``kind`` is ``p32``,
+        ``exp_avg`` or ``exp_avg_sq``.  Only the pieces in local chunks are
+        returned (client.py access_data on a CHUNK_BASED fp32 param)."""
+        idx = {"p32": 0, "exp_avg": 1, "exp_avg_sq": 2}[kind]
+        info = self.layout.tensor(name)
+        cs = self.layout.chunk_size
+        out = []
+        c, off, rest, done = info.chunk_id, info.start_offset, info.numel, 0
+        while rest > 0:
+            take = min(rest, cs - off)
+            if self.layout.is_local(c, self.rank):
+                k = self.local_ids.index(c)
+                out.append((self.chunk_state(k)[idx][off:off + take], done))
+            rest -= take
+            done += take
+            c += 1
+            off = 0
+        return out
+
+    # -------------------------------------------------------------- collectives
+    def reduce_scatter_group(self, group_id, async_op=False):
+        """SUM reduce-scatter of one communication group's fp16 chunks, in place
+        (see ``comm.reduce_scatter_group``)."""
+        if self.world_size == 1:
+            return None
+        return comm.reduce_scatter_group(self.fp16_group(group_id), self.rank, self.world_size,
+                                         self.layout.chunk_size, self.process_group, async_op)
+
+    def all_gather_group(self, group_id, async_op=False):
+        """All-gather of one communication group's fp16 param chunks, in place."""
+        if self.world_size == 1:
+            return None
+        return comm.all_gather_group(self.fp16_group(group_id), self.rank, self.world_size,
+                                     self.layout.chunk_size, self.process_group, async_op)
+
+    def all_reduce_flag(self, flag):
+        """MAX all-reduce of the overflow flag; stays on the device (the reference
+        follows it with `.item()`, fp16_cpu_adam.py:297)."""
+        if self.world_size == 1:
+            return
+        comm.all_reduce_flag(flag, self.process_group)

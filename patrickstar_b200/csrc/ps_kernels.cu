@@ -1,0 +1,1116 @@
+// B200 (sm_100a) kernels and C ABI of the chunk optimizer step.
+//
+// The arithmetic follows the reference's CPU Adam lane by lane
+// (patrickstar/ops/csrc/adam/cpu_adam.cpp:33-144): every step is one correctly
+// rounded IEEE binary32 operation, spelled with the round-to-nearest
+// intrinsics so that nvcc neither fuses nor reorders anything.  The file must
+// be compiled without --use_fast_math (no flush-to-zero, precise division and
+// square root).
+//
+// All kernels are streaming and HBM-bound: 128-bit coalesced loads and stores
+// with evict-first hints, several independent loads in flight per thread,
+// grids sized from the SM count.  There is no contraction, hence no tensor
+// core work.
+#include "ps_b200.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVec = 8;  // elements per 128-bit fp16 load
+
+thread_local int g_last_cuda_error = 0;
+std::atomic<uint64_t> g_launches{0};
+
+// ---------------------------------------------------------------------------
+// tuning knobs (ps_tune)
+// ---------------------------------------------------------------------------
+struct Tuning {
+    int unroll = 2;        // 128-bit groups per thread per tile (1, 2 or 4)
+    int blocks_per_sm = 0; // 0 = as many as the occupancy calculator allows
+    int scan_unroll = 4;
+};
+Tuning g_tune;
+
+#define PS_CUDA(call)                              \
+    do {                                           \
+        cudaError_t e__ = (call);                  \
+        if (e__ != cudaSuccess) {                  \
+            g_last_cuda_error = (int)e__;          \
+            cudaGetLastError();                    \
+            return PS_ERR_CUDA;                    \
+        }                                          \
+    } while (0)
+
+inline int after_launch()
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return PS_ERR_CUDA;
+    }
+    return PS_OK;
+}
+
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+};
+
+int device_info(DeviceInfo* out)
+{
+    static std::mutex mu;
+    static std::unordered_map<int, int> sm_by_device;
+    int dev = 0;
+    PS_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = sm_by_device.find(dev);
+    if (it == sm_by_device.end()) {
+        int sms = 0;
+        PS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        it = sm_by_device.emplace(dev, sms).first;
+    }
+    out->device = dev;
+    out->sm_count = it->second;
+    return PS_OK;
+}
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+struct Slot {
+    float loss_scale, beta1, beta2, b1m1, b2m1, bias2_sqrt, eps, step_size, wd, w_decay, clip,
+        divisor;
+    int adamw;
+};
+
+__device__ __forceinline__ Slot load_slot(const ps_hyper_slot* s)
+{
+    // plain loads: the slot lives in global memory (chunk-level kernel) or in
+    // shared memory (tensor-level kernel)
+    const uint4* q = reinterpret_cast<const uint4*>(s);
+    uint4 a = q[0], b = q[1], c = q[2], d = q[3];
+    Slot r;
+    r.loss_scale = __uint_as_float(a.x);
+    r.beta1 = __uint_as_float(a.y);
+    r.beta2 = __uint_as_float(a.z);
+    r.b1m1 = __uint_as_float(a.w);
+    r.b2m1 = __uint_as_float(b.x);
+    r.bias2_sqrt = __uint_as_float(b.y);
+    r.eps = __uint_as_float(b.z);
+    r.step_size = __uint_as_float(b.w);
+    r.wd = __uint_as_float(c.x);
+    r.w_decay = __uint_as_float(c.y);
+    r.clip = __uint_as_float(c.z);
+    r.divisor = __uint_as_float(c.w);
+    r.adamw = (int)d.x;
+    return r;
+}
+
+__device__ __forceinline__ Slot slot_from_value(const ps_hyper_slot& s)
+{
+    Slot r;
+    r.loss_scale = s.loss_scale;
+    r.beta1 = s.beta1;
+    r.beta2 = s.beta2;
+    r.b1m1 = s.beta1_minus1;
+    r.b2m1 = s.beta2_minus1;
+    r.bias2_sqrt = s.bias2_sqrt;
+    r.eps = s.eps;
+    r.step_size = s.step_size;
+    r.wd = s.weight_decay;
+    r.w_decay = s.w_decay;
+    r.clip = s.clip;
+    r.divisor = s.grad_divisor;
+    r.adamw = s.adamw_mode;
+    return r;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t h)
+{
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+__device__ __forceinline__ uint32_t float_to_half_bits(float f)
+{
+    return (uint32_t)__half_as_ushort(__float2half_rn(f));
+}
+
+// fp16 gradient as the step sees it: the fp16 `payload /= world_size` of
+// patrickstar/core/client.py:838 and the fp16 clamp_ of
+// patrickstar/ops/fp16_cpu_adam.py:365-379, each rounded back to fp16.
+__device__ __forceinline__ float grad_from_half(uint32_t h, const Slot& s)
+{
+    float g = half_bits_to_float(h);
+    if (s.divisor > 1.f) g = half_bits_to_float(float_to_half_bits(__fdiv_rn(g, s.divisor)));
+    if (s.clip > 0.f) g = half_bits_to_float(float_to_half_bits(fminf(fmaxf(g, -s.clip), s.clip)));
+    return g;
+}
+
+// One element of Adam_Optimizer::Step's SIMD body (cpu_adam.cpp:91-143).
+__device__ __forceinline__ void adam_element(float g, float& p, float& m, float& v, const Slot& s)
+{
+    if (s.loss_scale > 0.f) g = __fdiv_rn(g, s.loss_scale);
+    if (s.wd > 0.f && !s.adamw) g = __fmaf_rn(p, s.wd, g);
+    m = __fmul_rn(m, s.beta1);
+    m = __fmaf_rn(g, s.b1m1, m);
+    v = __fmul_rn(v, s.beta2);
+    g = __fmul_rn(g, g);
+    v = __fmaf_rn(g, s.b2m1, v);
+    g = __fsqrt_rn(v);
+    g = __fmaf_rn(g, s.bias2_sqrt, s.eps);
+    g = __fdiv_rn(m, g);
+    if (s.wd > 0.f && s.adamw) p = __fmaf_rn(p, s.w_decay, p);
+    p = __fmaf_rn(g, s.step_size, p);
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+
+// Index (absolute, in the segment table) of the last segment of [lo, hi) whose
+// start is <= e; lo when none starts at or before e.
+__device__ __forceinline__ uint32_t find_segment(const ps_segment* segs, uint32_t lo, uint32_t hi,
+                                                 uint32_t e)
+{
+    uint32_t a = lo, b = hi;  // invariant: answer in [a, b)
+    while (b - a > 1) {
+        uint32_t mid = a + ((b - a) >> 1);
+        if (segs[mid].start <= e)
+            a = mid;
+        else
+            b = mid;
+    }
+    return a;
+}
+
+struct SegView {
+    uint32_t start, end, slot;
+};
+__device__ __forceinline__ SegView load_segment(const ps_segment* segs, uint32_t i)
+{
+    uint4 q = *reinterpret_cast<const uint4*>(segs + i);
+    return SegView{q.x, q.y, q.z};
+}
+
+// Element-wise path for a group of up to 8 elements that is ragged (chunk end)
+// or straddles a segment boundary.  Scalar loads and stores; every element
+// looks up its own segment.
+template <bool kRestore, bool kGradHalf>
+__device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads,
+                                        const ps_segment* segs, uint32_t seg_lo, uint32_t seg_hi,
+                                        const ps_hyper_slot* slots, uint32_t e, uint32_t e_end,
+                                        uint32_t si, uint16_t* p16_out)
+{
+    for (uint32_t i = e; i < e_end; ++i) {
+        SegView sv = load_segment(segs, si);
+        while (i >= sv.end && si + 1 < seg_hi) {
+            ++si;
+            sv = load_segment(segs, si);
+        }
+        if (i < sv.start || i >= sv.end) continue;
+        float p = d.p32[i];
+        if (kRestore) {
+            if (p16_out) p16_out[i] = (uint16_t)float_to_half_bits(p);
+            continue;
+        }
+        Slot s = load_slot(slots + sv.slot);
+        float g;
+        if (kGradHalf)
+            g = grad_from_half(reinterpret_cast<const uint16_t*>(grads)[i], s);
+        else
+            g = reinterpret_cast<const float*>(grads)[i];
+        float m = d.exp_avg[i], v = d.exp_avg_sq[i];
+        adam_element(g, p, m, v, s);
+        d.p32[i] = p;
+        d.exp_avg[i] = m;
+        d.exp_avg_sq[i] = v;
+        if (p16_out) p16_out[i] = (uint16_t)float_to_half_bits(p);
+    }
+}
+
+// One tile of one chunk: U groups of 8 elements per thread, group j of thread t
+// at tile_base + (j * kThreads + t) * 8, so that every warp-wide access is one
+// contiguous 512-byte (fp16) or 2 x 512-byte (fp32) run.  All loads of the tile
+// are issued before the first dependent instruction.
+template <int U, bool kRestore, bool kWrite16>
+__device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segment* segs,
+                                          const ps_hyper_slot* slots, uint32_t tile_base)
+{
+    uint4 gq[U];
+    float4 pq[U][2], mq[U][2], vq[U][2];
+    uint32_t e[U];
+    bool full[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        e[j] = tile_base + (uint32_t)(j * kThreads + threadIdx.x) * kVec;
+        full[j] = (e[j] + kVec <= d.numel);
+        if (full[j]) {
+            const float4* pp = reinterpret_cast<const float4*>(d.p32 + e[j]);
+            pq[j][0] = ld_stream(pp);
+            pq[j][1] = ld_stream(pp + 1);
+            if (!kRestore) {
+                gq[j] = ld_stream(reinterpret_cast<const uint4*>(d.h16 + e[j]));
+                const float4* mp = reinterpret_cast<const float4*>(d.exp_avg + e[j]);
+                const float4* vp = reinterpret_cast<const float4*>(d.exp_avg_sq + e[j]);
+                mq[j][0] = ld_stream(mp);
+                mq[j][1] = ld_stream(mp + 1);
+                vq[j][0] = ld_stream(vp);
+                vq[j][1] = ld_stream(vp + 1);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        if (e[j] >= d.numel) continue;
+        uint32_t si = d.seg_begin;
+        if (d.seg_end - d.seg_begin > 1) si = find_segment(segs, d.seg_begin, d.seg_end, e[j]);
+        SegView sv = load_segment(segs, si);
+        if (!(full[j] && sv.start <= e[j] && e[j] + kVec <= sv.end)) {
+            uint32_t e_end = e[j] + kVec < d.numel ? e[j] + kVec : d.numel;
+            slow_group<kRestore, true>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e[j], e_end,
+                                       si, kWrite16 ? d.h16 : nullptr);
+            continue;
+        }
+        float p[8] = {pq[j][0].x, pq[j][0].y, pq[j][0].z, pq[j][0].w,
+                      pq[j][1].x, pq[j][1].y, pq[j][1].z, pq[j][1].w};
+        if (!kRestore) {
+            Slot s = load_slot(slots + sv.slot);
+            float m[8] = {mq[j][0].x, mq[j][0].y, mq[j][0].z, mq[j][0].w,
+                          mq[j][1].x, mq[j][1].y, mq[j][1].z, mq[j][1].w};
+            float v[8] = {vq[j][0].x, vq[j][0].y, vq[j][0].z, vq[j][0].w,
+                          vq[j][1].x, vq[j][1].y, vq[j][1].z, vq[j][1].w};
+            uint32_t gw[4] = {gq[j].x, gq[j].y, gq[j].z, gq[j].w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                uint32_t h = (k & 1) ? (gw[k >> 1] >> 16) : (gw[k >> 1] & 0xffffu);
+                adam_element(grad_from_half(h, s), p[k], m[k], v[k], s);
+            }
+            float4* pp = reinterpret_cast<float4*>(d.p32 + e[j]);
+            float4* mp = reinterpret_cast<float4*>(d.exp_avg + e[j]);
+            float4* vp = reinterpret_cast<float4*>(d.exp_avg_sq + e[j]);
+            st_stream(pp, make_float4(p[0], p[1], p[2], p[3]));
+            st_stream(pp + 1, make_float4(p[4], p[5], p[6], p[7]));
+            st_stream(mp, make_float4(m[0], m[1], m[2], m[3]));
+            st_stream(mp + 1, make_float4(m[4], m[5], m[6], m[7]));
+            st_stream(vp, make_float4(v[0], v[1], v[2], v[3]));
+            st_stream(vp + 1, make_float4(v[4], v[5], v[6], v[7]));
+        }
+        if (!kWrite16) continue;
+        uint4 out;
+        out.x = float_to_half_bits(p[0]) | (float_to_half_bits(p[1]) << 16);
+        out.y = float_to_half_bits(p[2]) | (float_to_half_bits(p[3]) << 16);
+        out.z = float_to_half_bits(p[4]) | (float_to_half_bits(p[5]) << 16);
+        out.w = float_to_half_bits(p[6]) | (float_to_half_bits(p[7]) << 16);
+        st_stream(reinterpret_cast<uint4*>(d.h16 + e[j]), out);
+    }
+}
+
+__device__ __forceinline__ ps_chunk_desc load_desc(const ps_chunk_desc* c)
+{
+    const uint4* q = reinterpret_cast<const uint4*>(c);
+    uint4 a = __ldg(q), b = __ldg(q + 1), w = __ldg(q + 2);
+    ps_chunk_desc d;
+    d.p32 = reinterpret_cast<float*>(((unsigned long long)a.y << 32) | a.x);
+    d.exp_avg = reinterpret_cast<float*>(((unsigned long long)a.w << 32) | a.z);
+    d.exp_avg_sq = reinterpret_cast<float*>(((unsigned long long)b.y << 32) | b.x);
+    d.h16 = reinterpret_cast<uint16_t*>(((unsigned long long)b.w << 32) | b.z);
+    d.numel = w.x;
+    d.seg_begin = w.y;
+    d.seg_end = w.z;
+    d.reserved = w.w;
+    return d;
+}
+
+// The fused chunk step over a table of chunks.  Tiles are numbered chunk-major;
+// consecutive CTAs take consecutive tiles, then stride by the grid.
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+chunk_step_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                  uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
+                  const ps_step_ctrl* __restrict__ ctrl)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    const int skip = __ldg(&ctrl->skip);
+    const ps_hyper_slot* slots = ctrl->slots;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+        const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+        const ps_chunk_desc d = load_desc(chunks + c);
+        const uint32_t tile_base = lt * kTile;
+        if (tile_base >= d.numel) continue;
+        if (skip)
+            step_tile<U, true, true>(d, segs, slots, tile_base);
+        else
+            step_tile<U, false, true>(d, segs, slots, tile_base);
+    }
+}
+
+// Tensor-level variant (image of adam_update): `d` holds the four pointers
+// advanced past `head` (0..7) leading elements so that all of them are 16-byte
+// aligned; d.numel counts the elements from there on.  The leading elements are
+// updated one per thread by block 0.
+template <int U, bool kWrite16>
+__global__ void __launch_bounds__(kThreads)
+tensor_step_kernel(ps_chunk_desc d, uint32_t head, ps_hyper_slot slot, uint32_t n_tiles)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    __shared__ __align__(16) ps_segment s_seg;
+    __shared__ __align__(16) ps_hyper_slot s_slot;
+    if (threadIdx.x == 0) {
+        s_seg = ps_segment{0u, d.numel, 0u, 0u};
+        s_slot = slot;
+    }
+    __syncthreads();
+    d.seg_begin = 0;
+    d.seg_end = 1;
+    if (blockIdx.x == 0 && threadIdx.x < head) {
+        const Slot s = slot_from_value(slot);
+        const int i = -(int)head + (int)threadIdx.x;
+        float p = d.p32[i], m = d.exp_avg[i], v = d.exp_avg_sq[i];
+        adam_element(grad_from_half(d.h16[i], s), p, m, v, s);
+        d.p32[i] = p;
+        d.exp_avg[i] = m;
+        d.exp_avg_sq[i] = v;
+        if (kWrite16) d.h16[i] = (uint16_t)float_to_half_bits(p);
+    }
+    for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const uint32_t tile_base = t * kTile;
+        if (tile_base >= d.numel) continue;
+        step_tile<U, false, kWrite16>(d, &s_seg, &s_slot, tile_base);
+    }
+}
+
+// Element-wise kernel for adam_update arguments the vector path cannot take:
+// fp32 gradients, a separate fp16 output, or pointers that are not mutually
+// 16-byte co-aligned.
+template <bool kGradHalf>
+__global__ void __launch_bounds__(kThreads)
+tensor_step_scalar_kernel(float* p32, const void* grads, float* exp_avg, float* exp_avg_sq, size_t n,
+                          ps_hyper_slot slot, uint16_t* p16_out)
+{
+    const Slot s = slot_from_value(slot);
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * kThreads) {
+        float g;
+        if (kGradHalf)
+            g = grad_from_half(reinterpret_cast<const uint16_t*>(grads)[i], s);
+        else
+            g = reinterpret_cast<const float*>(grads)[i];
+        float p = p32[i], m = exp_avg[i], v = exp_avg_sq[i];
+        adam_element(g, p, m, v, s);
+        p32[i] = p;
+        exp_avg[i] = m;
+        exp_avg_sq[i] = v;
+        if (p16_out) p16_out[i] = (uint16_t)float_to_half_bits(p);
+    }
+}
+
+// inf/nan test on packed halves: a half is inf or nan when its five exponent
+// bits are all set.
+__device__ __forceinline__ uint32_t nonfinite2(uint32_t w)
+{
+    return __vcmpeq2(w & 0x7c007c00u, 0x7c007c00u);
+}
+
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+overflow_scan_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                     uint32_t tiles_per_chunk, int32_t* __restrict__ flag)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t found = 0;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+        const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+        const uint16_t* h16 = reinterpret_cast<const uint16_t*>(
+            __ldg(reinterpret_cast<const unsigned long long*>(&chunks[c].h16)));
+        const uint32_t numel = __ldg(&chunks[c].numel);
+        const uint32_t tile_base = lt * kTile;
+        if (tile_base >= numel) continue;
+        uint4 q[U];
+        uint32_t e[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            e[j] = tile_base + (uint32_t)(j * kThreads + threadIdx.x) * kVec;
+            q[j] = make_uint4(0, 0, 0, 0);
+            if (e[j] + kVec <= numel) q[j] = ld_stream(reinterpret_cast<const uint4*>(h16 + e[j]));
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            found |= nonfinite2(q[j].x) | nonfinite2(q[j].y) | nonfinite2(q[j].z) | nonfinite2(q[j].w);
+            if (e[j] < numel && e[j] + kVec > numel) {
+                for (uint32_t i = e[j]; i < numel; ++i) found |= ((h16[i] & 0x7c00u) == 0x7c00u);
+            }
+        }
+    }
+    if (__syncthreads_or(found != 0) && threadIdx.x == 0) atomicOr(flag, 1);
+}
+
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+overflow_scan_buffer_kernel(const uint16_t* __restrict__ g, size_t n, size_t head, int32_t* flag)
+{
+    // [0, head) and the ragged tail are read element-wise by block 0; the
+    // 16-byte aligned body [head, head + 8 * n_vec) is read as uint4.
+    uint32_t found = 0;
+    const size_t n_vec = (n - head) / kVec;
+    const uint4* body = reinterpret_cast<const uint4*>(g + head);
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec;
+         i += (size_t)gridDim.x * kThreads) {
+        uint4 q = ld_stream(body + i);
+        found |= nonfinite2(q.x) | nonfinite2(q.y) | nonfinite2(q.z) | nonfinite2(q.w);
+    }
+    if (blockIdx.x == 0) {
+        for (size_t i = threadIdx.x; i < head; i += kThreads) found |= ((g[i] & 0x7c00u) == 0x7c00u);
+        for (size_t i = head + n_vec * kVec + threadIdx.x; i < n; i += kThreads)
+            found |= ((g[i] & 0x7c00u) == 0x7c00u);
+    }
+    if (__syncthreads_or(found != 0) && threadIdx.x == 0) atomicOr(flag, 1);
+}
+
+// ---------------------------------------------------------------------------
+// step-begin: skip decision, step counter, beta^t history, hyper slots,
+// loss-scale update.  One thread.
+// ---------------------------------------------------------------------------
+__device__ void derive_slot(ps_hyper_slot* out, const ps_group_hyper& g, float b1t, float b2t,
+                            int bias_correction, float loss_scale, float clip, float divisor)
+{
+    // update_state (cpu_adam.h:163-175)
+    float bc1 = 1.0f, bc2 = 1.0f;
+    if (bias_correction == 1) {
+        bc1 = __fsub_rn(1.0f, b1t);
+        bc2 = __fdiv_rn(1.0f, __fsqrt_rn(__fsub_rn(1.0f, b2t)));
+    }
+    // Adam_Optimizer::Step prologue (cpu_adam.cpp:42-46)
+    out->loss_scale = loss_scale;
+    out->beta1 = g.beta1;
+    out->beta2 = g.beta2;
+    out->beta1_minus1 = __fsub_rn(1.0f, g.beta1);
+    out->beta2_minus1 = __fsub_rn(1.0f, g.beta2);
+    out->bias2_sqrt = bc2;
+    out->eps = g.eps;
+    out->step_size = __fdiv_rn(-g.lr, bc1);
+    out->weight_decay = g.weight_decay;
+    out->w_decay = __fmul_rn(-g.lr, g.weight_decay);
+    out->clip = clip;
+    out->grad_divisor = divisor;
+    out->adamw_mode = g.adamw_mode;
+    out->reserved[0] = out->reserved[1] = out->reserved[2] = 0;
+}
+
+__device__ void pow_lookup(const float* tab, uint64_t tab_len, int group, uint64_t t, float beta1,
+                           float beta2, float* b1t, float* b2t, int32_t* error)
+{
+    if (tab != nullptr && t < tab_len) {
+        const float* e = tab + 2 * ((uint64_t)group * tab_len + t);
+        *b1t = e[0];
+        *b2t = e[1];
+    } else {
+        // the host keeps the table ahead of the step counter; reaching this is a
+        // host bug, reported through the sticky error word
+        *error |= 1;
+        *b1t = (float)pow((double)beta1, (double)t);
+        *b2t = (float)pow((double)beta2, (double)t);
+    }
+}
+
+// DynamicLossScaler.update_scale (loss_scaler.py:158-182)
+__device__ void scaler_update(ps_scaler_state* sc, int overflow)
+{
+    if (sc->dynamic <= 0) return;
+    if (overflow) {
+        if (sc->delayed_shift == 1 || sc->cur_hysteresis == 1) {
+            sc->cur_scale = fmax(sc->cur_scale / sc->scale_factor, sc->min_scale);
+        } else {
+            sc->cur_hysteresis -= 1;
+        }
+        sc->last_overflow_iter = sc->cur_iter;
+    } else {
+        if (sc->consecutive_hysteresis) sc->cur_hysteresis = sc->delayed_shift;
+        if ((sc->cur_iter - sc->last_overflow_iter) % sc->scale_window == 0) {
+            if (!sc->consecutive_hysteresis) sc->cur_hysteresis = sc->delayed_shift;
+            sc->cur_scale *= sc->scale_factor;
+        }
+    }
+    sc->cur_iter += 1;
+}
+
+__global__ void scaler_update_kernel(ps_scaler_state* sc, int32_t* flag, int overflow_host)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int overflow = flag != nullptr ? (*flag != 0) : (overflow_host != 0);
+    scaler_update(sc, overflow);
+    if (flag != nullptr) *flag = 0;
+}
+
+__global__ void step_begin_kernel(ps_step_ctrl* ctrl, ps_scaler_state* sc, int32_t* flag,
+                                  ps_step_plan plan, const float* pow_tab, uint64_t tab_len)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    // FP16Adam.check_overflow only ever sets the flag with a dynamic scaler
+    // (LossScaler.has_overflow is constant False, loss_scaler.py:61-62)
+    int overflow = (sc->dynamic > 0 && flag != nullptr && *flag != 0) ? 1 : 0;
+    const float loss_scale = (sc->dynamic < 0) ? -1.0f : (float)sc->cur_scale;
+    float clip = 0.f;
+    if (plan.clip > 0.0) {
+        double c = plan.clip;
+        if (sc->dynamic >= 0) c *= sc->cur_scale;
+        clip = (float)fmin(65504.0, c);
+    }
+    if (overflow) {
+        // fp16_cpu_adam.py:549-558: early return, state["step"] untouched
+        ctrl->skip = 1;
+        ctrl->n_skipped += 1;
+    } else {
+        ctrl->skip = 0;
+        const uint64_t t = ++ctrl->step;  // fp16_cpu_adam.py:574
+        // first adam_update call of the step: IncrementStep (cpu_adam.h:143-162)
+        const ps_group_hyper g0 = plan.groups[plan.first_group];
+        float b1t = ctrl->betta1_t, b2t = ctrl->betta2_t;
+        if (plan.n_calls < 1) {
+            // a rank without local parameters makes no adam_update call
+        } else if (g0.beta1 != ctrl->betta1 || g0.beta2 != ctrl->betta2) {
+            ctrl->native_step = t;
+            ctrl->betta1 = g0.beta1;
+            ctrl->betta2 = g0.beta2;
+            pow_lookup(pow_tab, tab_len, plan.first_group, t, g0.beta1, g0.beta2, &b1t, &b2t,
+                       &ctrl->error);
+        } else {
+            ctrl->native_step += 1;
+            if (ctrl->native_step != t) {
+                pow_lookup(pow_tab, tab_len, plan.first_group, t, g0.beta1, g0.beta2, &b1t, &b2t,
+                           &ctrl->error);
+                ctrl->native_step = t;
+            } else {
+                b1t = __fmul_rn(b1t, g0.beta1);
+                b2t = __fmul_rn(b2t, g0.beta2);
+            }
+        }
+        ctrl->betta1_t = b1t;
+        ctrl->betta2_t = b2t;
+        derive_slot(&ctrl->slots[0], g0, b1t, b2t, plan.bias_correction, loss_scale, clip,
+                    plan.grad_divisor);
+        if (plan.n_calls >= 2) {
+            // every later call of the step finds _step == step already, or other
+            // betas: both branches recompute pow(beta, step)
+            for (int g = 0; g < plan.n_groups; ++g) {
+                float c1, c2;
+                pow_lookup(pow_tab, tab_len, g, t, plan.groups[g].beta1, plan.groups[g].beta2, &c1,
+                           &c2, &ctrl->error);
+                derive_slot(&ctrl->slots[1 + g], plan.groups[g], c1, c2, plan.bias_correction,
+                            loss_scale, clip, plan.grad_divisor);
+                if (g == plan.last_group) {
+                    ctrl->betta1 = plan.groups[g].beta1;
+                    ctrl->betta2 = plan.groups[g].beta2;
+                    ctrl->betta1_t = c1;
+                    ctrl->betta2_t = c2;
+                    ctrl->native_step = t;
+                }
+            }
+        }
+    }
+    scaler_update(sc, overflow);
+    if (flag != nullptr) *flag = 0;
+}
+
+__global__ void ctrl_init_kernel(ps_step_ctrl* ctrl, uint64_t step, float betta1, float betta2)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    ctrl->skip = 0;
+    ctrl->error = 0;
+    ctrl->step = step;
+    ctrl->n_skipped = 0;
+    // a fresh Adam_Optimizer: _step 0, betta^t 1 (cpu_adam.h:100-103); a resumed
+    // one takes the pow branch on its first call because _step + 1 != step
+    ctrl->native_step = 0;
+    ctrl->betta1 = betta1;
+    ctrl->betta2 = betta2;
+    ctrl->betta1_t = 1.0f;
+    ctrl->betta2_t = 1.0f;
+    ps_hyper_slot z;
+    memset(&z, 0, sizeof(z));
+    for (int i = 0; i < PS_MAX_SLOTS; ++i) ctrl->slots[i] = z;
+}
+
+__global__ void scaler_init_kernel(ps_scaler_state* sc, ps_scaler_state init)
+{
+    if (threadIdx.x == 0 && blockIdx.x == 0) *sc = init;
+}
+
+__global__ void scale_loss_kernel(const float* loss, float* out, size_t n, const ps_scaler_state* sc)
+{
+    // Python computes loss * cur_scale with the scale as a double scalar that
+    // torch converts to the tensor's dtype
+    const float s = (sc->dynamic < 0) ? 1.0f : (float)sc->cur_scale;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __fmul_rn(loss[i], s);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+
+// Host image of Adam_Optimizer's scalar state (cpu_adam.h:93-112, 143-175).
+struct AdamClock {
+    float alpha, betta1, betta2, eps, weight_decay;
+    float betta1_t = 1.0f, betta2_t = 1.0f;
+    size_t step = 0;
+    float bias_correction1 = 1.0f, bias_correction2 = 1.0f;
+    bool adamw_mode = true;
+
+    void increment_step(size_t s, float beta1, float beta2)
+    {
+        if (beta1 != betta1 || beta2 != betta2) {
+            step = s;
+            betta1 = beta1;
+            betta2 = beta2;
+            betta1_t = (float)std::pow((double)betta1, (double)s);
+            betta2_t = (float)std::pow((double)betta2, (double)s);
+        } else {
+            step++;
+            if (step != s) {
+                betta1_t = (float)std::pow((double)betta1, (double)s);
+                betta2_t = (float)std::pow((double)betta2, (double)s);
+                step = s;
+            } else {
+                betta1_t *= betta1;
+                betta2_t *= betta2;
+            }
+        }
+    }
+    void update_state(float lr, float epsilon, float wd, bool bias_correction)
+    {
+        alpha = lr;
+        eps = epsilon;
+        weight_decay = wd;
+        bias_correction1 = 1.0f;
+        bias_correction2 = 1.0f;
+        if (bias_correction) {
+            bias_correction1 = 1 - betta1_t;
+            bias_correction2 = 1 / sqrtf(1 - betta2_t);
+        }
+    }
+    ps_hyper_slot slot(float loss_scale) const
+    {
+        ps_hyper_slot s;
+        memset(&s, 0, sizeof(s));
+        s.loss_scale = loss_scale;
+        s.beta1 = betta1;
+        s.beta2 = betta2;
+        s.beta1_minus1 = 1 - betta1;
+        s.beta2_minus1 = 1 - betta2;
+        s.bias2_sqrt = bias_correction2;
+        s.eps = eps;
+        s.step_size = -1 * alpha / bias_correction1;
+        s.weight_decay = weight_decay;
+        s.w_decay = -1 * alpha * weight_decay;
+        s.clip = 0.f;
+        s.grad_divisor = 0.f;
+        s.adamw_mode = adamw_mode ? 1 : 0;
+        return s;
+    }
+};
+
+std::mutex g_opt_mu;
+std::unordered_map<int, std::shared_ptr<AdamClock>> g_optimizers;
+
+template <typename K>
+int grid_for(K kernel, uint64_t total_tiles, int* grid_out)
+{
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    int per_sm = g_tune.blocks_per_sm;
+    if (per_sm <= 0) {
+        PS_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0));
+        if (per_sm < 1) per_sm = 1;
+    }
+    uint64_t g = (uint64_t)di.sm_count * (uint64_t)per_sm;
+    if (g > total_tiles) g = total_tiles;
+    if (g < 1) g = 1;
+    *grid_out = (int)g;
+    return PS_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int U>
+int launch_chunk_step(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
+                      const ps_segment* segs, const ps_step_ctrl* ctrl, cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    uint64_t total = (uint64_t)tpc * n_chunks;
+    int grid = 1;
+    int rc = grid_for(chunk_step_kernel<U>, total, &grid);
+    if (rc != PS_OK) return rc;
+    chunk_step_kernel<U><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl);
+    return after_launch();
+}
+
+template <int U, bool kWrite16>
+int launch_tensor_step(const ps_chunk_desc& d, uint32_t head, const ps_hyper_slot& slot,
+                       cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tiles = (uint32_t)(((uint64_t)d.numel + kTile - 1) / kTile);
+    int grid = 1;
+    int rc = grid_for(tensor_step_kernel<U, kWrite16>, tiles ? tiles : 1, &grid);
+    if (rc != PS_OK) return rc;
+    tensor_step_kernel<U, kWrite16><<<grid, kThreads, 0, st>>>(d, head, slot, tiles);
+    return after_launch();
+}
+
+template <bool kWrite16>
+int launch_tensor_step_u(const ps_chunk_desc& d, uint32_t head, const ps_hyper_slot& slot,
+                         cudaStream_t st)
+{
+    switch (g_tune.unroll) {
+        case 1: return launch_tensor_step<1, kWrite16>(d, head, slot, st);
+        case 4: return launch_tensor_step<4, kWrite16>(d, head, slot, st);
+        default: return launch_tensor_step<2, kWrite16>(d, head, slot, st);
+    }
+}
+
+template <int U>
+int launch_scan(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel, int32_t* flag,
+                cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    uint64_t total = (uint64_t)tpc * n_chunks;
+    int grid = 1;
+    int rc = grid_for(overflow_scan_kernel<U>, total, &grid);
+    if (rc != PS_OK) return rc;
+    overflow_scan_kernel<U><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, flag);
+    return after_launch();
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int ps_version(void) { return 100; }
+
+const char* ps_strerror(int code)
+{
+    switch (code) {
+        case PS_OK: return "ok";
+        case PS_ERR_INVALID: return "invalid argument";
+        case PS_ERR_UNKNOWN_ID: return "unknown optimizer id";
+        case PS_ERR_ALIGN: return "pointer or offset not aligned as required";
+        case PS_ERR_CUDA: return "CUDA runtime call failed (see ps_last_cuda_error)";
+        case PS_ERR_TABLE: return "chunk/segment table failed validation";
+        case PS_ERR_LIMIT: return "stated maximum exceeded";
+        default: return "unknown error code";
+    }
+}
+
+int ps_last_cuda_error(void) { return g_last_cuda_error; }
+
+uint64_t ps_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int ps_tune(const char* key, int value)
+{
+    if (key == nullptr) return PS_ERR_INVALID;
+    if (!strcmp(key, "unroll")) {
+        if (value != 1 && value != 2 && value != 4) return PS_ERR_INVALID;
+        g_tune.unroll = value;
+    } else if (!strcmp(key, "blocks_per_sm")) {
+        if (value < 0 || value > 32) return PS_ERR_INVALID;
+        g_tune.blocks_per_sm = value;
+    } else if (!strcmp(key, "scan_unroll")) {
+        if (value != 1 && value != 2 && value != 4) return PS_ERR_INVALID;
+        g_tune.scan_unroll = value;
+    } else {
+        return PS_ERR_INVALID;
+    }
+    return PS_OK;
+}
+
+int ps_adam_create(int optimizer_id, float alpha, float betta1, float betta2, float eps,
+                   float weight_decay, int adamw_mode, int should_log)
+{
+    auto c = std::make_shared<AdamClock>();
+    c->alpha = alpha;
+    c->betta1 = betta1;
+    c->betta2 = betta2;
+    c->eps = eps;
+    c->weight_decay = weight_decay;
+    c->adamw_mode = adamw_mode != 0;
+    {
+        std::lock_guard<std::mutex> lk(g_opt_mu);
+        g_optimizers[optimizer_id] = c;
+    }
+    if (should_log) {
+        printf("Adam Optimizer #%d is created with sm_100a CUDA arithmetic capability.\n",
+               optimizer_id);
+        printf("Config: alpha=%f, betas=(%f, %f), weight_decay=%f, adam_w=%d\n", alpha, betta1,
+               betta2, weight_decay, adamw_mode ? 1 : 0);
+    }
+    return PS_OK;
+}
+
+int ps_adam_destroy(int optimizer_id)
+{
+    std::lock_guard<std::mutex> lk(g_opt_mu);
+    return g_optimizers.erase(optimizer_id) ? PS_OK : PS_ERR_UNKNOWN_ID;
+}
+
+int ps_adam_get_state(int optimizer_id, float out[4], uint64_t* step)
+{
+    if (out == nullptr || step == nullptr) return PS_ERR_INVALID;
+    std::lock_guard<std::mutex> lk(g_opt_mu);
+    auto it = g_optimizers.find(optimizer_id);
+    if (it == g_optimizers.end()) return PS_ERR_UNKNOWN_ID;
+    out[0] = it->second->betta1_t;
+    out[1] = it->second->betta2_t;
+    out[2] = it->second->bias_correction1;
+    out[3] = it->second->bias_correction2;
+    *step = it->second->step;
+    return PS_OK;
+}
+
+int ps_adam_update(int optimizer_id, size_t step, float lr, float beta1, float beta2, float epsilon,
+                   float weight_decay, int bias_correction, float* params_dev, const void* grads_dev,
+                   float* exp_avg_dev, float* exp_avg_sq_dev, size_t n, int g_is_half,
+                   float loss_scale, uint16_t* p16_out_dev, void* stream)
+{
+    std::shared_ptr<AdamClock> clock;
+    {
+        std::lock_guard<std::mutex> lk(g_opt_mu);
+        auto it = g_optimizers.find(optimizer_id);
+        if (it == g_optimizers.end()) return PS_ERR_UNKNOWN_ID;
+        clock = it->second;
+    }
+    if (n > 0 && (params_dev == nullptr || grads_dev == nullptr || exp_avg_dev == nullptr ||
+                  exp_avg_sq_dev == nullptr))
+        return PS_ERR_INVALID;
+    if (n >= 0x7fffff00ull) return PS_ERR_LIMIT;
+    const uintptr_t pa = (uintptr_t)params_dev, ma = (uintptr_t)exp_avg_dev,
+                    va = (uintptr_t)exp_avg_sq_dev, ga = (uintptr_t)grads_dev,
+                    oa = (uintptr_t)p16_out_dev;
+    if ((pa | ma | va) & 3u) return PS_ERR_ALIGN;
+    if (g_is_half ? (ga & 1u) : (ga & 3u)) return PS_ERR_ALIGN;
+    if (oa & 1u) return PS_ERR_ALIGN;
+    // the history-dependent state advances even for an empty tensor, as in the
+    // reference (ds_adam_step calls IncrementStep before looking at the size)
+    clock->increment_step(step, beta1, beta2);
+    clock->update_state(lr, epsilon, weight_decay, bias_correction == 1);
+    if (n == 0) return PS_OK;
+    const ps_hyper_slot slot = clock->slot(loss_scale);
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // Vector path: fp16 grads, fp16 output (if any) in the gradient's own
+    // storage, and a common number of leading elements `head` (0..7) after
+    // which all four arrays are 16-byte aligned.
+    bool vector_ok = g_is_half && (p16_out_dev == nullptr || oa == ga);
+    uint32_t head = 0;
+    if (vector_ok) {
+        head = (uint32_t)(((16u - (ga & 15u)) & 15u) >> 1);
+        const uintptr_t fwd32 = (uintptr_t)head * 4u;
+        vector_ok = (((pa + fwd32) | (ma + fwd32) | (va + fwd32)) & 15u) == 0;
+    }
+    if (vector_ok) {
+        if (head > n) head = (uint32_t)n;
+        ps_chunk_desc d;
+        d.p32 = params_dev + head;
+        d.exp_avg = exp_avg_dev + head;
+        d.exp_avg_sq = exp_avg_sq_dev + head;
+        d.h16 = reinterpret_cast<uint16_t*>(ga) + head;
+        d.numel = (uint32_t)(n - head);
+        d.seg_begin = 0;
+        d.seg_end = 1;
+        d.reserved = 0;
+        return p16_out_dev != nullptr ? launch_tensor_step_u<true>(d, head, slot, st)
+                                      : launch_tensor_step_u<false>(d, head, slot, st);
+    }
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    uint64_t blocks = (n + kThreads - 1) / kThreads;
+    uint64_t cap = (uint64_t)di.sm_count * 8u;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (g_is_half)
+        tensor_step_scalar_kernel<true><<<grid, kThreads, 0, st>>>(
+            params_dev, grads_dev, exp_avg_dev, exp_avg_sq_dev, n, slot, p16_out_dev);
+    else
+        tensor_step_scalar_kernel<false><<<grid, kThreads, 0, st>>>(
+            params_dev, grads_dev, exp_avg_dev, exp_avg_sq_dev, n, slot, p16_out_dev);
+    return after_launch();
+}
+
+int ps_table_check(const ps_chunk_desc* chunks, uint32_t n_chunks, const ps_segment* segs,
+                   uint32_t n_segs, uint32_t n_slots, uint32_t chunk_capacity)
+{
+    if (n_chunks > 0 && chunks == nullptr) return PS_ERR_INVALID;
+    if (n_segs > 0 && segs == nullptr) return PS_ERR_INVALID;
+    if (n_slots > PS_MAX_SLOTS) return PS_ERR_LIMIT;
+    if (chunk_capacity >= 0x7fffff00u) return PS_ERR_LIMIT;
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        const ps_chunk_desc& d = chunks[c];
+        if (!d.p32 || !d.exp_avg || !d.exp_avg_sq || !d.h16) return PS_ERR_INVALID;
+        if (!aligned16(d.p32) || !aligned16(d.exp_avg) || !aligned16(d.exp_avg_sq) ||
+            !aligned16(d.h16))
+            return PS_ERR_ALIGN;
+        if (d.numel > chunk_capacity) return PS_ERR_TABLE;
+        if (d.seg_begin > d.seg_end || d.seg_end > n_segs) return PS_ERR_TABLE;
+        if (d.seg_begin == d.seg_end && d.numel != 0) return PS_ERR_TABLE;
+        uint32_t prev_end = 0;
+        for (uint32_t s = d.seg_begin; s < d.seg_end; ++s) {
+            if (segs[s].start >= segs[s].end) return PS_ERR_TABLE;
+            if (segs[s].start < prev_end) return PS_ERR_TABLE;
+            if (segs[s].end > d.numel) return PS_ERR_TABLE;
+            if (segs[s].slot >= n_slots) return PS_ERR_TABLE;
+            prev_end = segs[s].end;
+        }
+    }
+    return PS_OK;
+}
+
+int ps_pow_table_fill(float beta1, float beta2, uint64_t t0, uint64_t count, float* out_host)
+{
+    if (count > 0 && out_host == nullptr) return PS_ERR_INVALID;
+    for (uint64_t i = 0; i < count; ++i) {
+        out_host[2 * i] = (float)std::pow((double)beta1, (double)(size_t)(t0 + i));
+        out_host[2 * i + 1] = (float)std::pow((double)beta2, (double)(size_t)(t0 + i));
+    }
+    return PS_OK;
+}
+
+int ps_ctrl_init(ps_step_ctrl* ctrl_dev, uint64_t step, float betta1, float betta2, void* stream)
+{
+    if (ctrl_dev == nullptr) return PS_ERR_INVALID;
+    if (!aligned16(ctrl_dev)) return PS_ERR_ALIGN;
+    ctrl_init_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctrl_dev, step, betta1, betta2);
+    return after_launch();
+}
+
+int ps_scaler_init(ps_scaler_state* scaler_dev, const ps_scaler_state* init_host, void* stream)
+{
+    if (scaler_dev == nullptr || init_host == nullptr) return PS_ERR_INVALID;
+    if (init_host->dynamic > 0 && (init_host->scale_window <= 0 || init_host->scale_factor <= 0.0))
+        return PS_ERR_INVALID;
+    scaler_init_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(scaler_dev, *init_host);
+    return after_launch();
+}
+
+int ps_overflow_scan(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                     int32_t* flag_dev, void* stream)
+{
+    if (flag_dev == nullptr) return PS_ERR_INVALID;
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_dev == nullptr) return PS_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (g_tune.scan_unroll) {
+        case 1: return launch_scan<1>(chunks_dev, n_chunks, max_numel, flag_dev, st);
+        case 2: return launch_scan<2>(chunks_dev, n_chunks, max_numel, flag_dev, st);
+        default: return launch_scan<4>(chunks_dev, n_chunks, max_numel, flag_dev, st);
+    }
+}
+
+int ps_overflow_scan_buffer(const uint16_t* g_dev, size_t n, int32_t* flag_dev, void* stream)
+{
+    if (flag_dev == nullptr) return PS_ERR_INVALID;
+    if (n == 0) return PS_OK;
+    if (g_dev == nullptr) return PS_ERR_INVALID;
+    if ((uintptr_t)g_dev & 1u) return PS_ERR_ALIGN;
+    size_t head = ((16u - ((uintptr_t)g_dev & 15u)) & 15u) >> 1;
+    if (head > n) head = n;
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    uint64_t n_vec = (n - head) / kVec;
+    uint64_t blocks = (n_vec + kThreads - 1) / kThreads;
+    uint64_t cap = (uint64_t)di.sm_count * 8u;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (grid < 1) grid = 1;
+    overflow_scan_buffer_kernel<1><<<grid, kThreads, 0, (cudaStream_t)stream>>>(g_dev, n, head,
+                                                                               flag_dev);
+    return after_launch();
+}
+
+int ps_step_begin(ps_step_ctrl* ctrl_dev, ps_scaler_state* scaler_dev, int32_t* flag_dev,
+                  const ps_step_plan* plan_host, const float* pow_table_dev, uint64_t pow_table_len,
+                  void* stream)
+{
+    if (ctrl_dev == nullptr || scaler_dev == nullptr || plan_host == nullptr) return PS_ERR_INVALID;
+    const ps_step_plan& p = *plan_host;
+    if (p.n_groups < 1 || p.n_groups > PS_MAX_GROUPS) return PS_ERR_LIMIT;
+    if (p.first_group < 0 || p.first_group >= p.n_groups || p.last_group < 0 ||
+        p.last_group >= p.n_groups || p.n_calls < 0)
+        return PS_ERR_INVALID;
+    step_begin_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctrl_dev, scaler_dev, flag_dev, p,
+                                                         pow_table_dev, pow_table_len);
+    return after_launch();
+}
+
+int ps_scaler_update(ps_scaler_state* scaler_dev, int32_t* flag_dev, int overflow_host, void* stream)
+{
+    if (scaler_dev == nullptr) return PS_ERR_INVALID;
+    scaler_update_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(scaler_dev, flag_dev, overflow_host);
+    return after_launch();
+}
+
+int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                  const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_dev == nullptr || segs_dev == nullptr || ctrl_dev == nullptr) return PS_ERR_INVALID;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (g_tune.unroll) {
+        case 1: return launch_chunk_step<1>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        case 4: return launch_chunk_step<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        default: return launch_chunk_step<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+    }
+}
+
+int ps_scaler_read(const ps_scaler_state* scaler_dev, ps_scaler_state* out_host, void* stream)
+{
+    if (scaler_dev == nullptr || out_host == nullptr) return PS_ERR_INVALID;
+    PS_CUDA(cudaMemcpyAsync(out_host, scaler_dev, sizeof(ps_scaler_state), cudaMemcpyDeviceToHost,
+                            (cudaStream_t)stream));
+    PS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return PS_OK;
+}
+
+int ps_ctrl_read(const ps_step_ctrl* ctrl_dev, ps_step_ctrl* out_host, void* stream)
+{
+    if (ctrl_dev == nullptr || out_host == nullptr) return PS_ERR_INVALID;
+    PS_CUDA(cudaMemcpyAsync(out_host, ctrl_dev, sizeof(ps_step_ctrl), cudaMemcpyDeviceToHost,
+                            (cudaStream_t)stream));
+    PS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return PS_OK;
+}
+
+int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scaler_state* scaler_dev,
+                  void* stream)
+{
+    if (n == 0) return PS_OK;
+    if (loss_dev == nullptr || out_dev == nullptr || scaler_dev == nullptr) return PS_ERR_INVALID;
+    uint64_t blocks = (n + 255) / 256;
+    int grid = (int)(blocks < 1024 ? blocks : 1024);
+    scale_loss_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(loss_dev, out_dev, n, scaler_dev);
+    return after_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,133 @@
+"""``initialize_engine`` — the reference's config surface for the optimizer step.
+
+Mirror of ``patrickstar/runtime/__init__.py:40-93`` and of the configuration
+half of ``PatrickStarEngine.__init__`` (``patrickstar/runtime/engine.py:53-126``):
+the same nested dict, keys, defaults and quirks.  The forward/backward wrappers
+of the reference engine (hooks, memory tracer, chunk eviction) serve model
+execution and are not rebuilt; ``ChunkStepEngine`` keeps only a thin
+forward / backward / step so that a small model can be trained end to end.
+
+Quirks kept on purpose (they decide the loss-scale trajectory):
+  * ``fp16.hysteresis`` is passed as the scaler's ``scale_factor`` and
+    ``delayed_shift`` stays 1 (engine.py:90-97): every overflow divides the
+    scale by ``hysteresis`` at once.
+  * ``fp16`` present requires ``enabled`` true and a ``loss_scale`` key
+    (engine.py:84-88); ``loss_scale == 0`` selects the dynamic scaler.
+  * ``config=None`` crashes in the reference (``None.get``,
+    runtime/__init__.py:74); here it means "all defaults".
+"""
+import torch
+
+from .chunk_list import DEFAULT_CHUNK_SIZE
+from .client import ChunkClient
+from .fp16_adam import FP16Adam
+from .loss_scaler import DynamicLossScaler, LossScaler
+
+_DEFAULT_OPTIM = {
+    "type": "Adam",
+    "params": {"lr": 0.01, "betas": (0.9, 0.999), "eps": 1e-8, "weight_decay": 0, "use_hybrid_adam": True},
+}
+
+
+def parse_config(config):
+    """engine.py:53-105 as a pure function.  Returns a dict with optim_type,
+    optim_params, scaler ("none" | ("static", scale) | ("dynamic", kwargs)),
+    gradient_clipping, default_chunk_size."""
+    out = {"default_chunk_size": DEFAULT_CHUNK_SIZE, "gradient_clipping": -1, "scaler": "none"}
+    if config is None:
+        out["optim_type"] = _DEFAULT_OPTIM["type"]
+        out["optim_params"] = dict(_DEFAULT_OPTIM["params"])
+        return out
+    out["default_chunk_size"] = config.get("default_chunk_size", DEFAULT_CHUNK_SIZE)
+    optim_config = config.get("optimizer", _DEFAULT_OPTIM)
+    optim_type = optim_config.get("type", _DEFAULT_OPTIM["type"])
+    if optim_type not in ["Adam", "AdamW"]:
+        raise ValueError(
+            f"Only support Adam and AdamW at the moment. Get optimizer type {optim_type}")
+    optim_params = dict(optim_config.get("params", _DEFAULT_OPTIM["params"]))
+    for key, val in _DEFAULT_OPTIM["params"].items():
+        if key not in optim_params:
+            optim_params[key] = val
+    out["optim_type"] = optim_type
+    out["optim_params"] = optim_params
+    if "fp16" in config:
+        ls = config["fp16"]
+        assert ls["enabled"], "Must enable fp16 training."
+        assert "loss_scale" in ls, "Must have `loss_scale` field set."
+        if ls["loss_scale"] == 0:
+            out["scaler"] = ("dynamic", dict(
+                init_scale=2 ** ls.get("initial_scale_power", 16),
+                scale_factor=ls.get("hysteresis", 2),
+                scale_window=ls.get("loss_scale_window", 2000),
+                min_scale=ls.get("min_loss_scale", 1)))
+        else:
+            out["scaler"] = ("static", ls["loss_scale"])
+    if "gradient_clipping" in config:
+        out["gradient_clipping"] = config["gradient_clipping"]
+    return out
+
+
+def build_loss_scaler(parsed, device=None):
+    s = parsed["scaler"]
+    if s == "none":
+        return None
+    if s[0] == "dynamic":
+        return DynamicLossScaler(device=device, **s[1])
+    return LossScaler(s[1], device=device)
+
+
+class ChunkStepEngine(torch.nn.Module):
+    """Thin stand-in for PatrickStarEngine: holds module, client, loss scaler and
+    optimizer; ``backward`` scales the loss and hands the gradients to the fp16
+    slots the way the reference's backward hook does
+    (patrickstar/core/hook.py:200-230)."""
+
+    def __init__(self, model, client, config):
+        super().__init__()
+        self.module = model
+        self.client = client
+        parsed = parse_config(config)
+        self.loss_scaler = build_loss_scaler(parsed, client.device)
+        self.gradient_clipping = parsed["gradient_clipping"]
+        op = parsed["optim_params"]
+        self.optimizer = FP16Adam(
+            client, self.module.parameters(), loss_scaler=self.loss_scaler,
+            gradient_clipping=self.gradient_clipping, lr=op["lr"], betas=op["betas"], eps=op["eps"],
+            weight_decay=op["weight_decay"], use_adamw=(parsed["optim_type"] == "AdamW"),
+            use_hybrid_adam=op["use_hybrid_adam"])
+
+    def forward(self, *inputs, **kwargs):
+        return self.module(*inputs, **kwargs)
+
+    def backward(self, loss):
+        """engine.py:206-224 + hook.py:212-216: scaled backward, per-parameter
+        overflow check, gradient copied into the parameter's fp16 slot."""
+        if self.loss_scaler is not None:
+            self.loss_scaler.backward(loss)
+        else:
+            loss.backward()
+        with torch.no_grad():
+            for p in self.module.parameters():
+                if p.grad is None:
+                    continue
+                self.optimizer.check_overflow(p)
+                p.data.copy_(p.grad)
+                p.grad = None
+
+
+def initialize_engine(model_func, local_rank, config=None, client=None):
+    """runtime/__init__.py:40-93.  Returns ``(engine, optimizer)``."""
+    if isinstance(model_func, torch.nn.Module):
+        assert client is not None, "Must pass the client when passing a nn.Module."
+        model = model_func
+    else:
+        assert callable(model_func), "model_func need to be callable."
+        parsed = parse_config(config)
+        client = ChunkClient(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
+                             config=(config or {}).get("client", None))
+        model = model_func()
+        model.to(dtype=torch.float16)
+        client.register_module(model)
+        client.allocate()
+    engine = ChunkStepEngine(model=model, client=client, config=config)
+    return (engine, engine.optimizer)
