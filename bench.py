@@ -1,0 +1,468 @@
+#!/usr/bin/env python
+"""Benchmark of the chunk optimizer step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the dynamic-loss-scale configuration — 16 chunks of 64 Mi
+elements, fp32 master ~ N(0, 0.02), exp_avg ~ N(0, 1e-4), exp_avg_sq = |N(0, 1e-6)|,
+fp16 grads = fp16(N(0, 1e-3) * scale), Adam lr 1e-3 betas (0.9, 0.999) eps 1e-6
+wd 0, DynamicLossScaler(2**3, window 1000, min 1).  One step = overflow scan of
+all chunks + step-begin kernel + the fused chunk step.  With N > 1 every rank
+owns 16 chunks of a 16*N chunk list (weak scaling) and a step additionally does
+the reduce-scatter of the fp16 grad chunks and the all-gather of the fp16 param
+chunks of every communication group.
+
+Prints ONE JSON line on rank 0.  All data is synthetic and seeded.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CHUNK = 64 * 1024 * 1024
+CHUNKS_PER_RANK = 16
+HYPER = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0)
+SCALER = dict(init_scale=2 ** 3, scale_factor=2, scale_window=1000, min_scale=1)
+METRIC = "adam_updated_params_per_sec"
+UNIT = "params/s"
+BYTES_PER_PARAM = 28  # fp16 grad 2 + fp32 p/m/v read 12 + write 12 + fp16 param 2
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunks", type=int, default=CHUNKS_PER_RANK, help="chunks per rank")
+    ap.add_argument("--chunk-size", type=int, default=CHUNK)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--unroll", type=int, default=0, help="kernel tuning knob (0 = library default)")
+    ap.add_argument("--blocks-per-sm", type=int, default=-1)
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while running."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline / reference arm
+# ---------------------------------------------------------------------------
+def _load_cpu_impl():
+    """The reference's own CPU Adam (oracle/_ref) when it was built, else the C
+    port of it."""
+    from oracle import port, ref
+    try:
+        mod = ref.load()
+        return "reference", mod
+    except (FileNotFoundError, ImportError, OSError):
+        port.lib()
+        return "port", port
+
+
+def cpu_chunk_inputs(n):
+    import torch
+    g = torch.Generator().manual_seed(0)
+    p = torch.randn(n, generator=g) * 0.02
+    m = torch.randn(n, generator=g) * 1e-4
+    v = (torch.randn(n, generator=g) * 1e-6).abs()
+    gr = (torch.randn(n, generator=g) * 1e-3 * 8).half()
+    return p, m, v, gr
+
+
+def cpu_adam_call(kind, impl, handle, step, p, g, m, v):
+    if kind == "reference":
+        impl.adam_update(handle, step, HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                         HYPER["weight_decay"], True, p, g, m, v, 8.0)
+    else:
+        handle.adam_update(step, HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                           HYPER["weight_decay"], True, p, g, m, v, 8.0)
+
+
+def cpu_baseline(n, calls=20, warm=3):
+    """Times adam_update of the CPU implementation on one chunk with all host
+    threads.  Bounded sample: 1 chunk, `calls` calls."""
+    import torch
+    kind, impl = _load_cpu_impl()
+    cores = torch.get_num_threads()
+    p, m, v, g = cpu_chunk_inputs(n)
+    if kind == "reference":
+        impl.create_adam(31337, HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                         HYPER["weight_decay"], False, False)
+        handle = 31337
+    else:
+        handle = impl.OracleAdam(HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                                 HYPER["weight_decay"], False)
+    for i in range(warm):
+        cpu_adam_call(kind, impl, handle, 1 + i, p, g, m, v)
+    ts = []
+    for i in range(calls):
+        t0 = time.perf_counter()
+        cpu_adam_call(kind, impl, handle, 1 + warm + i, p, g, m, v)
+        ts.append(time.perf_counter() - t0)
+    if kind == "reference":
+        impl.destroy_adam(31337)
+    ts.sort()
+    med = ts[len(ts) // 2]
+    return {"value": n / med, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": "1 chunk of %d elements, %d adam_update calls (median %.2f ms), all host threads; "
+                      "Adam only (26 B/param), no overflow scan, no fp16 write-back" % (n, calls, med * 1e3)}
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the whole step on the host cores:
+    per chunk the overflow test `grad.float().sum()` (loss_scaler.py:138), the
+    native adam_update, and the fp32 -> fp16 chunk cast (chunk_io_buff.py:123-126)."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, impl = _load_cpu_impl()
+    n, nchunks = args.chunk_size, args.chunks
+    cores = torch.get_num_threads()
+    p0, m0, v0, g0 = cpu_chunk_inputs(n)
+    # a bounded sample: `sample` chunks stand for the rank's `nchunks` (same distributions)
+    sample = min(nchunks, 4)
+    P = [p0.clone() for _ in range(sample)]
+    M = [m0.clone() for _ in range(sample)]
+    V = [v0.clone() for _ in range(sample)]
+    G = [g0.clone() for _ in range(sample)]
+    H = [torch.empty(n, dtype=torch.float16) for _ in range(sample)]
+    if kind == "reference":
+        impl.create_adam(31338, HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                         HYPER["weight_decay"], False, False)
+        handle = 31338
+    else:
+        handle = impl.OracleAdam(HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
+                                 HYPER["weight_decay"], False)
+
+    def one_step(step):
+        overflow = False
+        for k in range(sample):
+            s = float(G[k].float().sum())
+            overflow |= (s in (float("inf"), -float("inf")) or s != s)
+        for k in range(sample):
+            cpu_adam_call(kind, impl, handle, step, P[k], G[k], M[k], V[k])
+            H[k].copy_(P[k])
+        return overflow
+
+    for i in range(args.warmup):
+        one_step(1 + i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        one_step(1 + args.warmup + i)
+    dt = time.perf_counter() - t0
+    value = sample * n * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": "%d of %d chunks per step (overflow test + adam_update + fp16 cast), "
+                                   "all host threads" % (sample, nchunks)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, world):
+    return {"workload": "dynamic-loss-scale chunk step: %d chunks x %d elements per rank, Adam lr 1e-3 "
+                        "betas (0.9,0.999) eps 1e-6 wd 0, DynamicLossScaler(2^3, window 1000, min 1)"
+                        % (args.chunks, args.chunk_size),
+            "chunks_per_rank": args.chunks, "chunk_elements": args.chunk_size,
+            "parallelism": "chunk-sharded x%d" % world,
+            "collectives": "none" if world == 1 else "reduce-scatter fp16 grads + all-gather fp16 params per group",
+            "l2": "inputs (%.1f GiB per rank) exceed L2; fp16 grad slots rewritten between timed steps"
+                  % (args.chunks * args.chunk_size * 14 / 2 ** 30)}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus %d must be launched with torch.distributed.run "
+                             "--nproc-per-node %d" % (args.gpus, args.gpus))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
+    from patrickstar_b200 import _lib
+
+    if args.unroll:
+        _lib.tune("unroll", args.unroll)
+    if args.blocks_per_sm >= 0:
+        _lib.tune("blocks_per_sm", args.blocks_per_sm)
+
+    cs, npr = args.chunk_size, args.chunks
+    client = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat")
+    client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
+    client.allocate()
+    scaler = DynamicLossScaler(device=dev, **SCALER)
+    opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
+
+    # seeded synthetic state, generated on the device chunk by chunk
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    for k in range(npr):
+        p, m, v = client.chunk_state(k)
+        p.normal_(0, 0.02, generator=gen)
+        m.normal_(0, 1e-4, generator=gen)
+        v.normal_(0, 1e-6, generator=gen).abs_()
+    # pristine fp16 grads of one communication group (world chunks); copied into
+    # every group's slots before each step, outside the timed events
+    tmp = torch.empty(world * cs, dtype=torch.float32, device=dev)
+    tmp.normal_(0, 1e-3 * 8, generator=gen)
+    pristine = tmp.half()
+    del tmp
+
+    def refresh_grads():
+        for g in range(npr):
+            client.fp16_group(g).copy_(pristine)
+
+    def one_step():
+        if world > 1:
+            opt.step_with_collectives()
+        else:
+            opt.step()
+
+    kernel_ev = []
+
+    def timed_kernel_step():
+        """opt.step() with CUDA events around the fused chunk-step launch."""
+        orig = opt._update_resident
+
+        def wrapped(st, first=0, count=None):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            orig(st, first, count)
+            b.record()
+            kernel_ev.append((a, b, (client.n_resident - first) if count is None else count))
+        opt._update_resident = wrapped
+        try:
+            one_step()
+        finally:
+            opt._update_resident = orig
+
+    for _ in range(args.warmup):
+        refresh_grads()
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    step_ev = []
+    torch.cuda.synchronize()
+    for _ in range(args.steps):
+        refresh_grads()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        timed_kernel_step()
+        b.record()
+        step_ev.append((a, b))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    step_ms = [a.elapsed_time(b) for a, b in step_ev]
+    total_ms = sum(step_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ctrl = opt.read_ctrl()
+    assert ctrl.step == args.warmup + args.steps and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
+    params_per_step = npr * cs * world
+    value = params_per_step * args.steps / (total_ms * 1e-3)
+
+    kern_ms = [a.elapsed_time(b) for a, b, _ in kernel_ev]
+    kern_chunks = sum(c for _, _, c in kernel_ev)
+    kern_avg_ms = sum(kern_ms) / len(kern_ms)
+    peak, peak_kind = measured_peaks()
+    bytes_per_launch = BYTES_PER_PARAM * cs * (kern_chunks / len(kernel_ev))
+    achieved = bytes_per_launch / (kern_avg_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "chunk_step_kernel", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
+                "traffic": None, "algorithmic_bytes_per_launch": bytes_per_launch,
+                "launch_ms": kern_avg_ms, "launches_timed": len(kernel_ev)}
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, client, opt, pristine, world, rank, dev)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, world),
+            "roofline": roofline,
+            "clocks": clocks, "gpu_launches": int(launches),
+            "hbm_gbs_whole_step": (BYTES_PER_PARAM + 2) * npr * cs / (total_ms / args.steps * 1e-3) / 1e9
+            if world == 1 else None,
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(cs)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, client, opt, pristine, world, rank, dev):
+    """The same step through the public API with HOST buffers: every step copies
+    the rank's fp16 grads from pinned host memory into the fp16 slots, runs the
+    step, and copies the updated fp16 params of the local chunks plus the
+    control block back to pinned host memory."""
+    import torch
+    import torch.distributed as dist
+    cs, npr = args.chunk_size, args.chunks
+    steps = max(2, min(args.steps, 5))
+    host_in = torch.empty(world * cs, dtype=torch.float16).pin_memory()
+    host_in.copy_(pristine)
+    host_out = torch.empty(npr * cs, dtype=torch.float16).pin_memory()
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
+
+    def e2e_step():
+        evs = []
+        with torch.cuda.stream(copy_in):
+            for g in range(npr):
+                client.fp16_group(g).copy_(host_in, non_blocking=True)
+                e = torch.cuda.Event()
+                e.record()
+                evs.append(e)
+        for e in evs:
+            main.wait_event(e)
+        if world > 1:
+            opt.step_with_collectives()
+        else:
+            opt.step()
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            for k, cid in enumerate(client.local_ids):
+                host_out[k * cs:(k + 1) * cs].copy_(client.fp16_chunk(cid), non_blocking=True)
+        main.wait_stream(copy_out)
+        return opt.read_ctrl()  # device -> host read of the step's result (skip flag, step counter)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"value": npr * cs * world * steps / (ms * 1e-3), "unit": UNIT,
+            "h2d_bytes_per_step": 2 * npr * world * cs, "d2h_bytes_per_step": 2 * npr * cs + 1072,
+            "ms_per_step": ms / steps, "steps": steps,
+            "what": "pinned host fp16 grads -> slots, step, fp16 params of local chunks + control block -> pinned host"}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+"""GPU parity of the tensor-level entry point (the image of cpu_adam_op.adam_update)
+through the C ABI, against the reference's golden vectors and the CPU oracle.
+
+Bar: fp32 params / exp_avg / exp_avg_sq bit-exact (0 ulp; contract <= 2 ulp),
+fp16 params bit-exact (contract <= 1 ulp)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import n_bit_mismatch, ulp_diff_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def op():
+    from patrickstar_b200 import cpu_adam_op
+    return cpu_adam_op
+
+
+def test_golden_vectors_of_the_reference(op, golden_dir):
+    z = np.load(os.path.join(golden_dir, "adam_cases.npz"))
+    meta = json.loads(bytes(z["meta"]).decode())
+    dev = torch.device("cuda:0")
+    for ci, c in enumerate(meta):
+        k = c["key"]
+        p = torch.from_numpy(z[k + "_p0"].copy()).to(dev)
+        m = torch.from_numpy(z[k + "_m0"].copy()).to(dev)
+        v = torch.from_numpy(z[k + "_v0"].copy()).to(dev)
+        oid = 7000 + ci
+        op.create_adam(oid, c["lr"], c["betas"][0], c["betas"][1], c["eps"], c["wd"], c["adamw"], False)
+        for i, s in enumerate(c["steps"]):
+            g = torch.from_numpy(z["%s_g%d" % (k, i)].copy()).to(dev)
+            if c["hist"] == "seq":
+                op.adam_update(oid, s, c["lr"], *c["betas"], c["eps"], c["wd"], True, p, g, m, v, c["scale"])
+            else:
+                h = c["n"] // 2
+                for sl in (slice(0, h), slice(h, None)):
+                    op.adam_update(oid, s, c["lr"], *c["betas"], c["eps"], c["wd"], True, p[sl], g[sl],
+                                   m[sl], v[sl], c["scale"])
+        op.destroy_adam(oid)
+        assert n_bit_mismatch(p.cpu().numpy(), z[k + "_p"]) == 0, c
+        assert n_bit_mismatch(m.cpu().numpy(), z[k + "_m"]) == 0, c
+        assert n_bit_mismatch(v.cpu().numpy(), z[k + "_v"]) == 0, c
+
+
+@pytest.mark.parametrize("n", [0, 1, 7, 8, 1023, 1024, 4099, 1 << 20, (1 << 20) + 13])
+@pytest.mark.parametrize("offset", [0, 1, 3, 8])
+def test_shapes_offsets_and_fp16_writeback(op, oracle_port, n, offset):
+    """Ragged sizes and misaligned slices (the reference's own test uses (1023,)
+    and (1024, 32), unitest/test_ds_cpu_adam.py:175); fp16 write-back into the
+    gradient's storage."""
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(n * 31 + offset)
+    tot = n + offset + 16
+    P = torch.randn(tot, generator=gen) * 0.02
+    M = torch.randn(tot, generator=gen) * 1e-4
+    V = (torch.randn(tot, generator=gen) * 1e-6).abs()
+    G = (torch.randn(tot, generator=gen) * 1e-3 * 32).half()
+    sl = slice(offset, offset + n)
+    # oracle
+    p, m, v, g = P[sl].clone(), M[sl].clone(), V[sl].clone(), G[sl].clone()
+    o = oracle_port.OracleAdam(0.01, 0.9, 0.999, 1e-8, 0.001, True)
+    if n:
+        o.adam_update(1, 0.01, 0.9, 0.999, 1e-8, 0.001, True, p, g, m, v, 32.0)
+    # device
+    Pd, Md, Vd, Gd = P.to(dev), M.to(dev), V.to(dev), G.to(dev)
+    op.create_adam(7100, 0.01, 0.9, 0.999, 1e-8, 0.001, True, False)
+    op.adam_update(7100, 1, 0.01, 0.9, 0.999, 1e-8, 0.001, True, Pd[sl], Gd[sl], Md[sl], Vd[sl], 32.0,
+                   fp16_params_out=Gd[sl])
+    op.destroy_adam(7100)
+    torch.cuda.synchronize()
+    Pc, Mc, Vc, Gc = Pd.cpu(), Md.cpu(), Vd.cpu(), Gd.cpu()
+    assert ulp_diff_f32(Pc[sl].numpy(), p.numpy()) == 0
+    assert ulp_diff_f32(Mc[sl].numpy(), m.numpy()) == 0
+    assert ulp_diff_f32(Vc[sl].numpy(), v.numpy()) == 0
+    assert torch.equal(Gc[sl].view(torch.int16), p.half().view(torch.int16))
+    # nothing outside the slice moved
+    for full, orig in ((Pc, P), (Mc, M), (Vc, V), (Gc, G)):
+        assert torch.equal(full[:offset].view(torch.uint8), orig[:offset].view(torch.uint8))
+        assert torch.equal(full[offset + n:].view(torch.uint8), orig[offset + n:].view(torch.uint8))
+
+
+@pytest.mark.parametrize("ghalf", [True, False])
+@pytest.mark.parametrize("adamw", [True, False])
+def test_no_writeback_and_fp32_grads(op, oracle_port, ghalf, adamw):
+    dev = torch.device("cuda:0")
+    n = 50000
+    gen = torch.Generator().manual_seed(5)
+    p = torch.randn(n, generator=gen) * 0.02
+    m = torch.randn(n, generator=gen) * 1e-4
+    v = (torch.randn(n, generator=gen) * 1e-6).abs()
+    pd, md, vd = p.to(dev), m.to(dev), v.to(dev)
+    o = oracle_port.OracleAdam(1e-3, 0.9, 0.999, 1e-8, 0.01, adamw)
+    op.create_adam(7200, 1e-3, 0.9, 0.999, 1e-8, 0.01, adamw, False)
+    for step in range(1, 5):
+        g = torch.randn(n, generator=gen) * 1e-2
+        g = g.half() if ghalf else g
+        gd = g.to(dev)
+        o.adam_update(step, 1e-3, 0.9, 0.999, 1e-8, 0.01, True, p, g, m, v, -1)
+        op.adam_update(7200, step, 1e-3, 0.9, 0.999, 1e-8, 0.01, True, pd, gd, md, vd, -1)
+        assert torch.equal(gd.cpu().view(torch.uint8), g.view(torch.uint8))  # grads are read-only
+    op.destroy_adam(7200)
+    assert n_bit_mismatch(pd.cpu().numpy(), p.numpy()) == 0
+    assert n_bit_mismatch(md.cpu().numpy(), m.numpy()) == 0
+    assert n_bit_mismatch(vd.cpu().numpy(), v.numpy()) == 0
+
+
+def test_torch_adam_path_tolerance(op):
+    """The reference's own test (unitest/test_ds_cpu_adam.py:141-155): max |diff|
+    < 1e-4 against the torch re-statement of FP16Adam.torch_adam_update."""
+    import math
+    dev = torch.device("cuda:0")
+    for use_adamw in (False, True):
+        for shape in ((1023,), (1024, 32)):
+            for grad_dtype in (torch.float, torch.half):
+                for loss_scale in (-1, 2 ** 5):
+                    torch.manual_seed(0)
+                    p = torch.rand(shape, device=dev)
+                    g = torch.rand(shape, dtype=grad_dtype, device=dev)
+                    if loss_scale > 0:
+                        g.mul_(loss_scale)
+                    m = torch.rand(shape, device=dev)
+                    v = torch.rand(shape, device=dev)
+                    p2, g2, m2, v2 = p.clone(), g.clone().float(), m.clone(), v.clone()
+                    op.create_adam(7300, 0.01, 0.9, 0.999, 1e-8, 0.001, use_adamw, False)
+                    op.adam_update(7300, 1, 0.01, 0.9, 0.999, 1e-8, 0.001, True, p.view(-1), g.view(-1),
+                                   m.view(-1), v.view(-1), loss_scale)
+                    op.destroy_adam(7300)
+                    if loss_scale > 0:
+                        g2.div_(loss_scale)
+                    bc1, bc2 = 1 - 0.9, 1 - 0.999
+                    if use_adamw:
+                        p2.mul_(1 - 0.01 * 0.001)
+                    else:
+                        g2 = g2.add(p2, alpha=0.001)
+                    m2.mul_(0.9).add_(g2, alpha=0.1)
+                    v2.mul_(0.999).addcmul_(g2, g2, value=1 - 0.999)
+                    denom = (v2.sqrt() / math.sqrt(bc2)).add_(1e-8)
+                    p2.addcdiv_(m2, denom, value=-0.01 / bc1)
+                    assert (p - p2).abs().max() < 1e-4
+                    assert (m - m2).abs().max() < 1e-4
+                    assert (v - v2).abs().max() < 1e-4
+
+
+def test_error_codes(op):
+    from patrickstar_b200._lib import PSError, PS_ERR_UNKNOWN_ID
+    dev = torch.device("cuda:0")
+    x = torch.zeros(16, device=dev)
+    with pytest.raises(PSError) as e:
+        op.adam_update(99999, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, True, x, x.half(), x.clone(), x.clone(), -1)
+    assert e.value.code == PS_ERR_UNKNOWN_ID
+    with pytest.raises(PSError):
+        op.destroy_adam(99999)
+    with pytest.raises(TypeError):
+        op.adam_update(0, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, True, x.cpu(), x.half(), x, x, -1)
