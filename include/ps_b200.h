@@ -239,6 +239,46 @@ int ps_ctrl_read(const ps_step_ctrl* ctrl_dev, ps_step_ctrl* out_host, void* str
 int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scaler_state* scaler_dev,
                   void* stream);
 
+/* ------------------------------------------------------------------ */
+/* allocation-free variant                                              */
+/* ------------------------------------------------------------------ */
+#define PS_STATIC_MAX_CHUNKS 256u    /* chunk descriptors per call   */
+#define PS_STATIC_MAX_SEGMENTS 4096u /* segments per call            */
+
+/* No counterpart in the reference.  The same fused chunk step as
+ * ps_chunk_step, for callers that cannot call cudaMalloc: a host that has
+ * handed the whole GPU to its own pool and budgets every byte of it (the way
+ * PatrickStar's chunk manager and memory tracer do), or code on a latency
+ * path where cudaMalloc's device-wide synchronisation is not acceptable.  Such
+ * a caller has nowhere to put the device-side chunk table, segment table and
+ * control block that ps_chunk_step reads.  Here all three are taken from host
+ * memory and staged into a fixed array that lives inside the library's device
+ * image (about 81 KB on every GPU that loads the library, held until the
+ * process exits).  Nothing is allocated or freed, by this library or through
+ * any other.
+ *
+ *   chunks_host / segs_host : the tables of ps_chunk_step, in host memory; the
+ *                             pointers inside ps_chunk_desc are device
+ *                             addresses of the caller's chunks as before
+ *   slots_host[n_slots]     : the per-slot constants ps_step_begin would have
+ *                             prepared (n_slots <= PS_MAX_SLOTS)
+ *   skip                    : non-zero = restore the fp16 slots from the fp32
+ *                             master instead of updating
+ *
+ * Limits: n_chunks <= PS_STATIC_MAX_CHUNKS and n_segs <= PS_STATIC_MAX_SEGMENTS,
+ * else PS_ERR_LIMIT and nothing is enqueued; larger jobs are split by the
+ * caller.  The tables are validated like ps_table_check does.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls share the one array and each call overwrites it completely:
+ * calls on one stream are ordered and safe, calls that can overlap on the GPU
+ * (different streams, different threads) race on it and must be serialised by
+ * the caller.  The host tables may be reused as soon as the call returns. */
+int ps_chunk_step_static(const ps_chunk_desc* chunks_host, uint32_t n_chunks, uint32_t max_numel,
+                         const ps_segment* segs_host, uint32_t n_segs,
+                         const ps_hyper_slot* slots_host, uint32_t n_slots, int skip, void* stream);
+
 /* Tuning knobs for measurements: "unroll" (1, 2, 4: 128-bit groups per thread
  * per tile of the step kernels), "scan_unroll" (1, 2, 4), "blocks_per_sm"
  * (0 = occupancy calculator).  No counterpart in the reference. */

@@ -23,6 +23,8 @@ PS_ERR_LIMIT = -6
 
 PS_MAX_GROUPS = 15
 PS_MAX_SLOTS = PS_MAX_GROUPS + 1
+PS_STATIC_MAX_CHUNKS = 256
+PS_STATIC_MAX_SEGMENTS = 4096
 
 
 class PSError(RuntimeError):
@@ -101,6 +103,8 @@ SIGNATURES = {
     "ps_step_begin": (C.c_int, [_p, _p, _p, C.POINTER(StepPlan), _p, C.c_uint64, _p]),
     "ps_scaler_update": (C.c_int, [_p, _p, C.c_int, _p]),
     "ps_chunk_step": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p]),
+    "ps_chunk_step_static": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, C.c_uint32, _p, C.c_uint32,
+                                       C.c_int, _p]),
     "ps_scaler_read": (C.c_int, [_p, C.POINTER(ScalerState), _p]),
     "ps_ctrl_read": (C.c_int, [_p, C.POINTER(StepCtrl), _p]),
     "ps_scale_loss": (C.c_int, [_p, _p, C.c_size_t, _p, _p]),

@@ -801,6 +801,42 @@ int launch_scan(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_num
     return after_launch();
 }
 
+// ---------------------------------------------------------------------------
+// scratch of ps_chunk_step_static: control block, chunk table and segment table
+// of one call, resident in every context that loads this library.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticCtrlBytes = 1280;  // sizeof(ps_step_ctrl) rounded up to 256
+constexpr size_t kStaticChunkBytes = (size_t)PS_STATIC_MAX_CHUNKS * sizeof(ps_chunk_desc);
+constexpr size_t kStaticSegBytes = (size_t)PS_STATIC_MAX_SEGMENTS * sizeof(ps_segment);
+constexpr size_t kStaticChunkOff = kStaticCtrlBytes;
+constexpr size_t kStaticSegOff = kStaticChunkOff + kStaticChunkBytes;
+constexpr size_t kStaticBytes = kStaticSegOff + kStaticSegBytes;
+static_assert(sizeof(ps_step_ctrl) <= kStaticCtrlBytes, "control block outgrew its slot");
+static_assert(kStaticChunkOff % 256 == 0 && kStaticSegOff % 256 == 0, "tables must stay aligned");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the
+// symbol's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_address(unsigned char** out)
+{
+    static std::mutex mu;
+    static std::unordered_map<int, unsigned char*> by_device;
+    int dev = 0;
+    PS_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = by_device.find(dev);
+    if (it == by_device.end()) {
+        unsigned char* ptr = nullptr;
+        PS_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+        if (ptr == nullptr) return PS_ERR_CUDA;
+        it = by_device.emplace(dev, ptr).first;
+    }
+    *out = it->second;
+    return PS_OK;
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------
@@ -1111,6 +1147,43 @@ int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scal
     int grid = (int)(blocks < 1024 ? blocks : 1024);
     scale_loss_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(loss_dev, out_dev, n, scaler_dev);
     return after_launch();
+}
+
+int ps_chunk_step_static(const ps_chunk_desc* chunks_host, uint32_t n_chunks, uint32_t max_numel,
+                         const ps_segment* segs_host, uint32_t n_segs,
+                         const ps_hyper_slot* slots_host, uint32_t n_slots, int skip, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_host == nullptr || segs_host == nullptr || slots_host == nullptr) return PS_ERR_INVALID;
+    if (n_chunks > PS_STATIC_MAX_CHUNKS || n_segs > PS_STATIC_MAX_SEGMENTS || n_slots > PS_MAX_SLOTS)
+        return PS_ERR_LIMIT;
+    if (n_segs == 0 || n_slots == 0) return PS_ERR_INVALID;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    int rc = ps_table_check(chunks_host, n_chunks, segs_host, n_segs, n_slots, max_numel);
+    if (rc != PS_OK) return rc;
+    unsigned char* base = nullptr;
+    rc = static_scratch_address(&base);  // first call on a device: cudaGetSymbolAddress
+    if (rc != PS_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the whole control block is rebuilt on the host and overwritten, so nothing
+    // of the previous call survives in it
+    ps_step_ctrl ctrl;
+    memset(&ctrl, 0, sizeof(ctrl));
+    ctrl.skip = skip ? 1 : 0;
+    for (uint32_t i = 0; i < n_slots; ++i) ctrl.slots[i] = slots_host[i];
+    PS_CUDA(cudaMemcpyAsync(base, &ctrl, sizeof(ctrl), cudaMemcpyHostToDevice, st));
+    PS_CUDA(cudaMemcpyAsync(base + kStaticChunkOff, chunks_host, (size_t)n_chunks * sizeof(ps_chunk_desc),
+                            cudaMemcpyHostToDevice, st));
+    PS_CUDA(cudaMemcpyAsync(base + kStaticSegOff, segs_host, (size_t)n_segs * sizeof(ps_segment),
+                            cudaMemcpyHostToDevice, st));
+    const ps_chunk_desc* chunks_dev = reinterpret_cast<const ps_chunk_desc*>(base + kStaticChunkOff);
+    const ps_segment* segs_dev = reinterpret_cast<const ps_segment*>(base + kStaticSegOff);
+    const ps_step_ctrl* ctrl_dev = reinterpret_cast<const ps_step_ctrl*>(base);
+    switch (g_tune.unroll) {
+        case 1: return launch_chunk_step<1>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        case 4: return launch_chunk_step<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        default: return launch_chunk_step<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+    }
 }
 
 }  // extern "C"
