@@ -1,0 +1,119 @@
+"""The C-ABI library loads and exports every symbol include/ps_b200.h declares;
+host-only entry points behave (no compute call is made here: no GPU needed)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from patrickstar_b200 import build
+    build.build()
+    from patrickstar_b200 import _lib
+    return _lib
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "ps_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ps_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(L):
+    names = declared_functions()
+    assert len(names) >= 20
+    raw = C.CDLL(L.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), "symbol %s declared in ps_b200.h is not exported" % n
+        assert n in L.SIGNATURES, "symbol %s has no ctypes signature in _lib.py" % n
+    for n in L.SIGNATURES:
+        assert n in names, "%s bound in _lib.py but not declared in ps_b200.h" % n
+
+
+def test_struct_sizes_match_header_constants(L):
+    text = open(os.path.join(ROOT, "include", "ps_b200.h")).read()
+    assert int(re.search(r"#define PS_MAX_GROUPS (\d+)", text).group(1)) == L.PS_MAX_GROUPS
+    assert int(re.search(r"#define PS_STATIC_MAX_CHUNKS (\d+)", text).group(1)) == L.PS_STATIC_MAX_CHUNKS
+    assert int(re.search(r"#define PS_STATIC_MAX_SEGMENTS (\d+)", text).group(1)) == L.PS_STATIC_MAX_SEGMENTS
+    assert C.sizeof(L.StepCtrl) == 48 + 64 * (L.PS_MAX_GROUPS + 1)
+
+
+def test_host_only_entry_points(L):
+    lib = L.lib
+    assert lib.ps_version() >= 100
+    assert lib.ps_strerror(0) == b"ok"
+    assert b"unknown optimizer" in lib.ps_strerror(L.PS_ERR_UNKNOWN_ID)
+    assert lib.ps_adam_create(4242, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, 0) == 0
+    out = (C.c_float * 4)()
+    step = C.c_uint64()
+    assert lib.ps_adam_get_state(4242, out, C.byref(step)) == 0
+    assert (out[0], out[1], step.value) == (1.0, 1.0, 0)
+    assert lib.ps_adam_destroy(4242) == 0
+    assert lib.ps_adam_destroy(4242) == L.PS_ERR_UNKNOWN_ID
+    assert lib.ps_adam_get_state(4242, out, C.byref(step)) == L.PS_ERR_UNKNOWN_ID
+    assert lib.ps_tune(b"unroll", 3) == L.PS_ERR_INVALID
+    assert lib.ps_tune(b"nonsense", 1) == L.PS_ERR_INVALID
+    assert lib.ps_tune(b"unroll", 2) == 0
+
+
+def test_pow_table_is_the_libm_pow_of_the_reference(L):
+    """IncrementStep's pow branch: float(pow(double(float beta), step))
+    (patrickstar/ops/csrc/includes/cpu_adam.h:147-156)."""
+    import math
+    tab = np.zeros((300, 2), dtype=np.float32)
+    assert L.lib.ps_pow_table_fill(0.9, 0.999, 0, 300, tab.ctypes.data) == 0
+    b1, b2 = float(np.float32(0.9)), float(np.float32(0.999))
+    for t in (0, 1, 2, 10, 150, 299):
+        assert tab[t, 0] == np.float32(math.pow(b1, t))
+        assert tab[t, 1] == np.float32(math.pow(b2, t))
+
+
+def test_host_clock_matches_oracle_history(L):
+    """ps_adam_update advances the optimizer's beta^t history before it looks at
+    the tensors (as ds_adam_step does); with n == 0 that is all it does, so the
+    host state machine can be compared with the oracle's without a GPU."""
+    from oracle import port
+    lib = L.lib
+    seq = [(1, 0.9, 0.999), (2, 0.9, 0.999), (2, 0.9, 0.999), (3, 0.9, 0.999), (7, 0.9, 0.999),
+           (8, 0.9, 0.999), (8, 0.8, 0.99), (9, 0.8, 0.99), (9, 0.9, 0.999), (10, 0.9, 0.999)]
+    o = port.OracleAdam(1e-3, 0.9, 0.999, 1e-8, 0.0, True)
+    assert lib.ps_adam_create(4343, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, 0) == 0
+    empty32 = np.zeros(0, dtype=np.float32)
+    empty16 = np.zeros(0, dtype=np.float16)
+    out = (C.c_float * 4)()
+    step = C.c_uint64()
+    for s, b1, b2 in seq:
+        o.adam_update(s, 1e-3, b1, b2, 1e-8, 0.0, True, empty32, empty16, empty32, empty32, -1)
+        assert lib.ps_adam_update(4343, s, 1e-3, b1, b2, 1e-8, 0.0, 1, None, None, None, None, 0, 1, -1.0,
+                                  None, None) == 0
+        assert lib.ps_adam_get_state(4343, out, C.byref(step)) == 0
+        st = o.state()
+        got = [np.float32(x) for x in out]
+        want = [np.float32(st[k]) for k in ("betta1_t", "betta2_t", "bias_correction1", "bias_correction2")]
+        assert got == want and step.value == st["step"], (s, b1, b2)
+    lib.ps_adam_destroy(4343)
+
+
+def test_compute_entry_points_refuse_without_arguments(L):
+    lib = L.lib
+    assert lib.ps_overflow_scan(None, 1, 16, None, None) == L.PS_ERR_INVALID
+    assert lib.ps_chunk_step(None, 1, 16, None, None, None) == L.PS_ERR_INVALID
+    assert lib.ps_step_begin(None, None, None, None, None, 0, None) == L.PS_ERR_INVALID
+    assert lib.ps_adam_update(123456, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, None, None, 0, 1, -1.0,
+                              None, None) == L.PS_ERR_UNKNOWN_ID
+
+
+def test_package_import_is_lazy_and_fails_loudly_without_library(tmp_path, monkeypatch):
+    """No fallback: with the shared library missing, importing a compute name raises."""
+    import importlib
+    import sys
+    import patrickstar_b200
+    from patrickstar_b200 import _lib
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "missing.so"))
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _lib._load()

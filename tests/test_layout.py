@@ -1,0 +1,103 @@
+"""Chunk layout: packing rules, ownership, segment tables (host logic only).
+Modelled on the reference's unitest/test_chunk_tensor_index.py and
+unitest/test_chunk_data.py."""
+import numpy as np
+import pytest
+
+from patrickstar_b200.chunk_list import ChunkLayout
+
+
+def test_no_split_packing_like_the_reference():
+    # unitest/test_chunk_tensor_index.py:82-170: tensors never straddle; a module's list is atomic
+    lay = ChunkLayout(chunk_size=20, pack="no_split")
+    a = lay.append_tensor_list([("m1.w", 10, 0), ("m1.b", 2, 0)])
+    assert [(t.chunk_id, t.start_offset) for t in a] == [(0, 0), (0, 10)]
+    b = lay.append_tensor_list([("m2.w", 7, 0), ("m2.b", 2, 0)])   # 9 > 8 free -> new chunk as a whole
+    assert [(t.chunk_id, t.start_offset) for t in b] == [(1, 0), (1, 7)]
+    c = lay.append_tensor("m3.w", 11)
+    assert (c.chunk_id, c.start_offset) == (1, 9)
+    with pytest.raises(RuntimeError, match="larger than the chunk size"):
+        lay.append_tensor("huge", 21)
+    with pytest.raises(ValueError, match="duplicate"):
+        lay.append_tensor("m3.w", 1)
+    lay.freeze()
+    assert lay.n_data_chunks == 2 and lay.chunk_numel(0) == 12 and lay.chunk_numel(1) == 20
+
+
+def test_flat_packing_splits_tensors_at_chunk_boundaries():
+    lay = ChunkLayout(chunk_size=100, pack="flat")
+    lay.append_tensor_list([("a", 30, 0), ("b", 90, 1), ("c", 50, 0), ("big", 260, 1), ("d", 10, 0)])
+    lay.freeze()
+    assert lay.total_numel() == 440 and lay.n_data_chunks == 5
+    assert [lay.chunk_numel(c) for c in range(5)] == [100, 100, 100, 100, 40]
+    segs = {c: [(p.start, p.end, p.group) for p in lay.segments_of_chunk(c)] for c in range(5)}
+    assert segs[0] == [(0, 30, 0), (30, 100, 1)]
+    assert segs[1] == [(0, 20, 1), (20, 70, 0), (70, 100, 1)]
+    assert segs[2] == [(0, 100, 1)] and segs[3] == [(0, 100, 1)]
+    assert segs[4] == [(0, 30, 1), (30, 40, 0)]
+    # every element is covered exactly once
+    cover = np.zeros(500, dtype=int)
+    for c in range(5):
+        for s, e, _ in segs[c]:
+            cover[c * 100 + s:c * 100 + e] += 1
+    assert (cover[:440] == 1).all() and (cover[440:] == 0).all()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_ownership_and_padding(world):
+    # chunk_list.py:383-387: k-th chunk -> rank k % world, group k // world;
+    # preprocess.py:335-339: padded with dummy chunks to a multiple of world
+    lay = ChunkLayout(chunk_size=10, world_size=world, pack="flat")
+    lay.append_tensor("t", 10 * 11)
+    lay.freeze()
+    assert lay.n_data_chunks == 11
+    assert lay.n_chunks % world == 0 and lay.n_chunks - 11 < world
+    owned = [lay.local_chunk_ids(r) for r in range(world)]
+    assert sorted(sum(owned, [])) == list(range(lay.n_chunks))
+    assert len(set(len(o) for o in owned)) == 1 == (len(owned[0]) == lay.n_groups_comm)
+    for r in range(world):
+        for k, c in enumerate(owned[r]):
+            ci = lay.comm_info(c)
+            assert (ci.group_id, ci.offset) == (k, r)
+    for c in range(11, lay.n_chunks):
+        assert lay.is_dummy(c) and lay.chunk_numel(c) == 0 and lay.segments_of_chunk(c) == []
+
+
+def test_tables_first_call_slot_and_plan():
+    lay = ChunkLayout(chunk_size=100, world_size=2, pack="flat")
+    lay.append_tensor_list([("a", 30, 0), ("b", 90, 1), ("c", 50, 0), ("d", 10, 1)])
+    lay.freeze()
+    local, numels, ranges, segs = lay.build_tables(0)
+    assert local == [0] and numels == [100] and ranges == [(0, 2)]
+    assert segs.tolist() == [[0, 30, 0, 0], [30, 100, 2, 0]]      # first piece -> slot 0, group 1 -> slot 2
+    assert lay.plan_groups(0) == (0, 1, 2)
+    local, numels, ranges, segs = lay.build_tables(1)
+    assert local == [1] and numels == [80]
+    assert segs.tolist() == [[0, 20, 0, 0], [20, 70, 1, 0], [70, 80, 2, 0]]
+    assert lay.plan_groups(1) == (1, 1, 3)
+    # one single piece: it is the first call, slot 0
+    one = ChunkLayout(chunk_size=64, pack="flat")
+    one.append_tensor("w", 64)
+    one.freeze()
+    assert one.build_tables(0)[3].tolist() == [[0, 64, 0, 0]] and one.plan_groups(0) == (0, 0, 1)
+    # first piece merged with a same-group neighbour is split off again
+    two = ChunkLayout(chunk_size=64, pack="flat")
+    two.append_tensor_list([("w1", 10, 0), ("w2", 20, 0), ("b", 4, 1)])
+    two.freeze()
+    assert two.build_tables(0)[3].tolist() == [[0, 10, 0, 0], [10, 30, 1, 0], [30, 34, 2, 0]]
+
+
+def test_gpt2_xl_layout_counts():
+    """GPT-2 1.5B (48 layers, hidden 1600, vocab 50257, 1024 positions) packed flat
+    into 64 Mi-element chunks: 1,557,611,200 parameters -> 24 chunks."""
+    from patrickstar_b200.model_layouts import gpt_tensor_specs
+    specs = gpt_tensor_specs(n_layer=48, hidden=1600, vocab=50257, n_pos=1024)
+    lay = ChunkLayout(chunk_size=64 * 1024 * 1024, pack="flat")
+    lay.append_tensor_list([(n, int(np.prod(s)), g) for n, s, g in specs])
+    lay.freeze()
+    assert lay.total_numel() == 1557611200
+    assert lay.n_data_chunks == 24
+    groups = {g for _, _, g in specs}
+    assert groups == {0, 1}
+    n_decay = sum(int(np.prod(s)) for _, s, g in specs if g == 0)
+    assert n_decay == 48 * (1600 * 4800 + 1600 * 1600 + 1600 * 6400 + 6400 * 1600) + 50257 * 1600 + 1024 * 1600
