@@ -240,6 +240,45 @@ int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scal
                   void* stream);
 
 /* ------------------------------------------------------------------ */
+/* offload tier                                                         */
+/* ------------------------------------------------------------------ */
+#define PS_OFFLOAD_MAX_SLOTS 8
+
+/* One offloaded local chunk: its fp32 master / momentum / variance in PINNED
+ * host memory (what the reference keeps as CPU chunks under hybrid placement,
+ * patrickstar/ops/fp16_cpu_adam.py:523-528, patrickstar/core/chunk_data.py:275-366)
+ * and the index of its descriptor in the device chunk table.  That descriptor's
+ * p32 / exp_avg / exp_avg_sq must point at the staging slot (i % n_slots) the
+ * i-th chunk of a ps_offload_step call uses; its h16 / numel / segment range are
+ * the chunk's own. */
+typedef struct ps_offload_chunk {
+    float* p32_host;
+    float* exp_avg_host;
+    float* exp_avg_sq_host;
+    uint32_t numel;
+    uint32_t desc_index;
+} ps_offload_chunk;
+
+/* Creates the pipeline object: three side streams and 3 * n_slots + 1 events on
+ * the current device.  No device memory is allocated; the caller owns the
+ * staging slots.  n_slots = 2 is double buffering. */
+int ps_offload_create(void** pipeline_out, int n_slots);
+int ps_offload_destroy(void* pipeline);
+
+/* Streams n_chunks offloaded chunks through the staging slots around the fused
+ * chunk step, replacing the reference's synchronous chunk moves and CPU Adam
+ * for host-resident chunks (patrickstar/ops/chunk_io_buff.py:116-126, 241-247).
+ * staging_dev[3*s .. 3*s+2] = p32 / exp_avg / exp_avg_sq buffers of slot s, each
+ * at least numel floats.  Must be called after ps_step_begin on `stream`; the
+ * copies and kernels run on the pipeline's own streams, overlapped with whatever
+ * the caller enqueues on `stream` next, and `stream` is made to wait for the
+ * last write-back before the call returns (no host synchronisation). */
+int ps_offload_step(void* pipeline, const ps_offload_chunk* chunks_host, uint32_t n_chunks,
+                    float* const* staging_dev, const ps_chunk_desc* chunks_dev,
+                    const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, void* stream);
+int ps_offload_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ */
 /* allocation-free variant                                              */
 /* ------------------------------------------------------------------ */
 #define PS_STATIC_MAX_CHUNKS 256u    /* chunk descriptors per call   */

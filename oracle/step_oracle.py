@@ -61,8 +61,13 @@ class StepOracle:
         if not dynamic:
             overflow = False
         if overflow:
-            for h, p in zip(h16, p32):
-                port.cast_fp32_to_fp16(p, h.view(np.uint16))
+            # every local parameter's fp16 slot := cast(fp32 master).  (The reference
+            # copies chunk-wise, gaps included; gaps hold zeros on both sides there,
+            # so restoring the parameters' own elements is the same thing.)
+            for (c, s, e, _) in self.calls:
+                out = np.empty(e - s, dtype=np.uint16)
+                port.cast_fp32_to_fp16(np.ascontiguousarray(p32[c][s:e]), out)
+                h16[c].view(np.uint16)[s:e] = out
             self.scaler.update_scale(True)
             self.skipped += 1
             return True

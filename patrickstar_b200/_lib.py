@@ -40,7 +40,9 @@ CHUNK_DESC_DTYPE = np.dtype(
     [("p32", "<u8"), ("exp_avg", "<u8"), ("exp_avg_sq", "<u8"), ("h16", "<u8"),
      ("numel", "<u4"), ("seg_begin", "<u4"), ("seg_end", "<u4"), ("reserved", "<u4")])
 SEGMENT_DTYPE = np.dtype([("start", "<u4"), ("end", "<u4"), ("slot", "<u4"), ("reserved", "<u4")])
-assert CHUNK_DESC_DTYPE.itemsize == 48 and SEGMENT_DTYPE.itemsize == 16
+OFFLOAD_CHUNK_DTYPE = np.dtype([("p32_host", "<u8"), ("exp_avg_host", "<u8"), ("exp_avg_sq_host", "<u8"),
+                                ("numel", "<u4"), ("desc_index", "<u4")])
+assert CHUNK_DESC_DTYPE.itemsize == 48 and SEGMENT_DTYPE.itemsize == 16 and OFFLOAD_CHUNK_DTYPE.itemsize == 32
 
 
 class GroupHyper(C.Structure):
@@ -105,6 +107,10 @@ SIGNATURES = {
     "ps_chunk_step": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p]),
     "ps_chunk_step_static": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, C.c_uint32, _p, C.c_uint32,
                                        C.c_int, _p]),
+    "ps_offload_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
+    "ps_offload_destroy": (C.c_int, [_p]),
+    "ps_offload_step": (C.c_int, [_p, _p, C.c_uint32, _p, _p, _p, _p, _p]),
+    "ps_offload_last_cuda_error": (C.c_int, []),
     "ps_scaler_read": (C.c_int, [_p, C.POINTER(ScalerState), _p]),
     "ps_ctrl_read": (C.c_int, [_p, C.POINTER(StepCtrl), _p]),
     "ps_scale_loss": (C.c_int, [_p, _p, C.c_size_t, _p, _p]),

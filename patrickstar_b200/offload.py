@@ -1,0 +1,68 @@
+"""Host side of the offload tier: which local chunks are streamed, their staging
+slots and descriptors.  The pipeline itself (streams, events, copies, kernel
+launches) is native: ``ps_offload_step`` in ``csrc/ps_offload.cu``.
+
+The reference decides per step how many chunks fit on the GPU for Adam
+(``margin_chunk_num_for_gpu_adam``, patrickstar/ops/fp16_cpu_adam.py:523-528)
+and updates the others with its CPU Adam.  Here the split is fixed at
+allocation (``ChunkClient.allocate(state_budget_bytes=...)``): the first
+``n_resident`` local chunks stay in HBM, the others live in pinned host memory
+and are updated by the same GPU kernel through ``n_slots`` staging slots.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import CHUNK_DESC_DTYPE, OFFLOAD_CHUNK_DTYPE, check, lib
+
+
+class OffloadPipeline:
+    def __init__(self, client, optimizer, n_slots=2):
+        self.client = client
+        self.opt = optimizer
+        self.n_slots = n_slots
+        cs = client.layout.chunk_size
+        dev = client.device
+        n_off = len(client.local_ids) - client.n_resident
+        self.n_off = n_off
+        # staging slots: 3 fp32 chunk buffers each
+        self.staging = [[torch.empty(cs, dtype=torch.float32, device=dev) for _ in range(3)]
+                        for _ in range(n_slots)]
+        self._staging_ptrs = (C.c_void_p * (3 * n_slots))(
+            *[t.data_ptr() for slot in self.staging for t in slot])
+        # descriptors of the offloaded chunks: state pointers -> staging slot (i % n_slots)
+        desc = optimizer._desc_host.copy()
+        jobs = np.zeros(n_off, dtype=OFFLOAD_CHUNK_DTYPE)
+        for i in range(n_off):
+            k = client.n_resident + i
+            s = i % n_slots
+            desc["p32"][k], desc["exp_avg"][k], desc["exp_avg_sq"][k] = (
+                t.data_ptr() for t in self.staging[s])
+            p, m, v = client.chunk_state(k)
+            jobs[i] = (p.data_ptr(), m.data_ptr(), v.data_ptr(), int(desc["numel"][k]), k)
+        self._jobs = jobs
+        check(lib.ps_table_check(desc.ctypes.data, len(desc), optimizer._segs_host.ctypes.data,
+                                 len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
+              "ps_table_check")
+        optimizer._desc_host = desc
+        optimizer._desc_dev = torch.from_numpy(desc.view(np.uint8).copy()).to(dev)
+        self._handle = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(lib.ps_offload_create(C.byref(self._handle), n_slots), "ps_offload_create")
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h is not None and h.value:
+            lib.ps_offload_destroy(h)
+            self._handle = C.c_void_p()
+
+    def run(self):
+        """Enqueue the streamed update of every offloaded chunk (after ps_step_begin)."""
+        if self.n_off == 0:
+            return
+        opt = self.opt
+        with torch.cuda.device(self.client.device):
+            check(lib.ps_offload_step(self._handle, self._jobs.ctypes.data, self.n_off, self._staging_ptrs,
+                                      opt._desc_dev.data_ptr(), opt._segs_dev.data_ptr(),
+                                      opt._ctrl.data_ptr(), opt._stream()), "ps_offload_step")

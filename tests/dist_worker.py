@@ -1,0 +1,104 @@
+"""Worker of the multi-GPU chunk-step test.  Launched by
+tests/test_gpu_multi.py with torch.distributed.run, one rank per GPU (NCCL)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from helpers import n_bit_mismatch
+    from oracle.scaler_oracle import DynamicScalerOracle
+    from oracle.step_oracle import StepOracle
+    from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
+
+    cs = 1 << 15
+    n_tensors = 3 * world + 1          # -> padded with dummy chunks
+    client = ChunkClient(rank=local, default_chunk_size=cs, world_size=world, device=dev, pack="flat")
+    client.append_tensor_list([("w%d" % i, cs - (7 if i == n_tensors - 1 else 0), i % 2)
+                               for i in range(n_tensors)])
+    client.allocate()
+    lay = client.layout
+    assert lay.n_chunks % world == 0 and client.rank == rank
+    g0 = [p for n, p in client.params.items() if lay.tensor(n).group == 0]
+    g1 = [p for n, p in client.params.items() if lay.tensor(n).group == 1]
+    scaler = DynamicLossScaler(init_scale=8, scale_factor=2, scale_window=1000, min_scale=1, device=dev)
+    opt = FP16Adam(client, [{"params": g0, "weight_decay": 0.01}, {"params": g1, "weight_decay": 0.0}],
+                   loss_scaler=scaler, lr=1e-3, eps=1e-6, use_adamw=True)
+    gen = torch.Generator().manual_seed(500 + rank)
+    P, M, V = [], [], []
+    for k in range(len(client.local_ids)):
+        p = torch.randn(cs, generator=gen) * 0.02
+        m = torch.randn(cs, generator=gen) * 1e-4
+        v = (torch.randn(cs, generator=gen) * 1e-6).abs()
+        for dst, src in zip(client.chunk_state(k), (p, m, v)):
+            dst.copy_(src)
+        P.append(p.numpy().copy()), M.append(m.numpy().copy()), V.append(v.numpy().copy())
+    so = DynamicScalerOracle(8, 2, 1000, 1)
+    calls = [(client.local_ids.index(p.chunk_id), p.start, p.end, p.group) for p in lay.calls_of_rank(rank)]
+    groups = [{"lr": 1e-3, "betas": (0.9, 0.999), "eps": 1e-6, "weight_decay": 0.01},
+              {"lr": 1e-3, "betas": (0.9, 0.999), "eps": 1e-6, "weight_decay": 0.0}]
+    orc = StepOracle(calls, groups, so, True, world_size=world)
+    for step in range(4):
+        grads = (torch.randn(lay.n_chunks * cs, generator=gen) * 1e-3 * so.loss_scale * world).half()
+        poisoned = step == 2
+        if poisoned and rank == world - 1:
+            grads[cs + 5] = float("nan")          # one rank's local gradient overflows
+        client.fp16.copy_(grads)
+        # what the reduce-scatter leaves in this rank's chunks (computed with NCCL itself,
+        # so that its summation order is not part of the parity claim)
+        probe = client.fp16.clone()
+        for g in range(lay.n_groups_comm):
+            buf = probe[g * world * cs:(g + 1) * world * cs]
+            dist.reduce_scatter_tensor(buf[rank * cs:(rank + 1) * cs], buf, op=dist.ReduceOp.SUM)
+        # and it is the fp16-rounded exact sum within one fp16 ulp
+        allg = [torch.empty_like(grads, device=dev) for _ in range(world)]
+        dist.all_gather(allg, grads.to(dev))
+        exact = sum(t.double() for t in allg)
+        H = []
+        for c in client.local_ids:
+            got = probe[c * cs:(c + 1) * cs]
+            if not poisoned:
+                want = exact[c * cs:(c + 1) * cs]
+                tol = torch.maximum(want.abs() * 2.0 ** -10, torch.full_like(want, 2.0 ** -24))
+                assert ((got.double() - want).abs() <= tol).all(), "reduce-scatter off by more than 1 ulp"
+            H.append(got.cpu().numpy().copy())
+        opt.step_with_collectives()
+        flag = torch.tensor([int(poisoned)], device=dev)
+        skipped = orc.step(H, P, M, V, overflow=poisoned)
+        assert skipped == poisoned
+        torch.cuda.synchronize()
+        for k, c in enumerate(client.local_ids):
+            dp, dm, dv = client.chunk_state(k)
+            assert n_bit_mismatch(dp.cpu().numpy(), P[k]) == 0, (step, "p32", k)
+            assert n_bit_mismatch(dm.cpu().numpy(), M[k]) == 0, (step, "exp_avg", k)
+            assert n_bit_mismatch(dv.cpu().numpy(), V[k]) == 0, (step, "exp_avg_sq", k)
+            assert n_bit_mismatch(client.fp16_chunk(c).cpu().numpy(), H[k]) == 0, (step, "fp16", k)
+        # after the all-gather every rank holds every owner's chunk
+        mine = torch.cat([client.fp16_chunk(c) for c in client.local_ids]).view(torch.int16)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        for r in range(world):
+            theirs = torch.cat([client.fp16_chunk(c) for c in lay.local_chunk_ids(r)]).view(torch.int16)
+            assert torch.equal(theirs, gathered[r]), (step, "all-gather", r)
+    assert opt.step_count == 3 and opt.skipped_steps == 1 and scaler.loss_scale == 4
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("dist_worker ok: world %d" % world)
+
+
+if __name__ == "__main__":
+    main()
