@@ -76,7 +76,6 @@ def main():
                 assert ((got.double() - want).abs() <= tol).all(), "reduce-scatter off by more than 1 ulp"
             H.append(got.cpu().numpy().copy())
         opt.step_with_collectives()
-        flag = torch.tensor([int(poisoned)], device=dev)
         skipped = orc.step(H, P, M, V, overflow=poisoned)
         assert skipped == poisoned
         torch.cuda.synchronize()
@@ -87,12 +86,12 @@ def main():
             assert n_bit_mismatch(dv.cpu().numpy(), V[k]) == 0, (step, "exp_avg_sq", k)
             assert n_bit_mismatch(client.fp16_chunk(c).cpu().numpy(), H[k]) == 0, (step, "fp16", k)
         # after the all-gather every rank holds every owner's chunk
-        mine = torch.cat([client.fp16_chunk(c) for c in client.local_ids]).view(torch.int16)
+        mine = torch.cat([client.fp16_chunk(c) for c in client.local_ids])
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         for r in range(world):
-            theirs = torch.cat([client.fp16_chunk(c) for c in lay.local_chunk_ids(r)]).view(torch.int16)
-            assert torch.equal(theirs, gathered[r]), (step, "all-gather", r)
+            theirs = torch.cat([client.fp16_chunk(c) for c in lay.local_chunk_ids(r)])
+            assert torch.equal(theirs.view(torch.int16), gathered[r].view(torch.int16)), (step, "all-gather", r)
     assert opt.step_count == 3 and opt.skipped_steps == 1 and scaler.loss_scale == 4
     dist.barrier()
     dist.destroy_process_group()
