@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--unroll", type=int, default=0, help="kernel tuning knob (0 = library default)")
     ap.add_argument("--blocks-per-sm", type=int, default=-1)
+    ap.add_argument("--scan", default="local", choices=["local", "reduced"],
+                    help="N > 1: overflow test on local gradients before the reduction (the reference's "
+                         "rule) or on the reduced ones")
     return ap.parse_args()
 
 
@@ -303,7 +306,7 @@ def run_ours(args):
 
     def one_step():
         if world > 1:
-            opt.step_with_collectives()
+            opt.step_with_collectives(scan=args.scan)
         else:
             opt.step()
 
@@ -359,6 +362,7 @@ def run_ours(args):
         total_ms = float(t.item())
     ctrl = opt.read_ctrl()
     assert ctrl.step == args.warmup + args.steps and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
+    launches_note = launches
     params_per_step = npr * cs * world
     value = params_per_step * args.steps / (total_ms * 1e-3)
 
@@ -372,6 +376,26 @@ def run_ours(args):
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
                 "traffic": None, "algorithmic_bytes_per_launch": bytes_per_launch,
                 "launch_ms": kern_avg_ms, "launches_timed": len(kernel_ev)}
+
+    local_step = None
+    if world > 1:
+        # the rank-local part alone (scan of the owned chunks + step-begin + fused
+        # step, no collectives), for reading the comm-inclusive number against
+        ev = []
+        for _ in range(min(args.steps, 5)):
+            refresh_grads()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            opt.step()
+            b.record()
+            ev.append((a, b))
+        torch.cuda.synchronize()
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in ev)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        local_step = {"value": params_per_step * len(ev) / (float(t.item()) * 1e-3), "unit": UNIT,
+                      "ms_per_step": float(t.item()) / len(ev),
+                      "what": "rank-local part only: no reduce-scatter, no all-gather"}
 
     e2e = None
     if not args.no_e2e:
@@ -390,6 +414,9 @@ def run_ours(args):
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if local_step is not None:
+            line["local_step"] = local_step
+            line["config"]["overflow_scan"] = args.scan
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cs)
         print(json.dumps(line))
@@ -423,7 +450,7 @@ def run_e2e(args, client, opt, pristine, world, rank, dev):
         for e in evs:
             main.wait_event(e)
         if world > 1:
-            opt.step_with_collectives()
+            opt.step_with_collectives(scan=args.scan)
         else:
             opt.step()
         done = torch.cuda.Event()

@@ -40,6 +40,15 @@ class ChunkClient:
         self.rank = (torch.distributed.get_rank(process_group)
                      if world_size > 1 and torch.distributed.is_initialized() else 0)
         self.process_group = process_group
+        # Separate communicators for the two chunk collectives, so that the
+        # reduce-scatter of one communication group and the all-gather of another
+        # can be in flight together (collectives of one communicator serialise).
+        self.pg_reduce_scatter = self.pg_all_gather = process_group
+        if world_size > 1 and torch.distributed.is_initialized():
+            ranks = torch.distributed.get_process_group_ranks(
+                process_group if process_group is not None else torch.distributed.group.WORLD)
+            self.pg_reduce_scatter = torch.distributed.new_group(ranks)
+            self.pg_all_gather = torch.distributed.new_group(ranks)
         self.device = torch.device("cuda", rank) if device is None else torch.device(device)
         self.config = config or {}
         self.layout = ChunkLayout(default_chunk_size, world_size, pack)
@@ -178,14 +187,14 @@ class ChunkClient:
         if self.world_size == 1:
             return None
         return comm.reduce_scatter_group(self.fp16_group(group_id), self.rank, self.world_size,
-                                         self.layout.chunk_size, self.process_group, async_op)
+                                         self.layout.chunk_size, self.pg_reduce_scatter, async_op)
 
     def all_gather_group(self, group_id, async_op=False):
         """All-gather of one communication group's fp16 param chunks, in place."""
         if self.world_size == 1:
             return None
         return comm.all_gather_group(self.fp16_group(group_id), self.rank, self.world_size,
-                                     self.layout.chunk_size, self.process_group, async_op)
+                                     self.layout.chunk_size, self.pg_all_gather, async_op)
 
     def all_reduce_flag(self, flag):
         """MAX all-reduce of the overflow flag; stays on the device (the reference

@@ -227,39 +227,58 @@ class FP16Adam(torch.optim.Optimizer):
                                 self._segs_dev.data_ptr(), self._ctrl.data_ptr(), st), "ps_chunk_step")
 
     @torch.no_grad()
-    def step_with_collectives(self):
-        """The 8-GPU chunk step: per communication group a reduce-scatter of the
-        fp16 grad chunks, then the rank-local fused step, then an all-gather of
-        the fp16 param chunks (patrickstar/core/client.py:818-856, 428-497).
-        Collectives run on the process group's stream and are chained to the
-        step stream with events, so the scan of group g overlaps the
-        reduce-scatter of group g+1, and the all-gather of group g overlaps the
-        update of group g+1.  The skip decision needs the flag of every group on
-        every rank, so no update starts before the last scan."""
+    def step_with_collectives(self, scan="local"):
+        """The multi-GPU chunk step: per communication group a reduce-scatter of the
+        fp16 grad chunks, the rank-local fused step, and an all-gather of the fp16
+        param chunks (patrickstar/core/client.py:818-856, 428-497).
+
+        ``scan="local"`` (default) is the reference's rule: the overflow test runs
+        on this rank's own gradients BEFORE the reduction (patrickstar/core/hook.py:212)
+        and the flag is MAX-all-reduced (fp16_cpu_adam.py:292-297).  The skip
+        decision is then known before the first reduce-scatter, so the groups
+        pipeline: reduce-scatter of group g+1, update of group g and all-gather of
+        group g-1 are in flight together (two communicators, events between
+        streams, no host synchronisation).
+
+        ``scan="reduced"`` tests the reduced gradients instead (additionally
+        catches an fp16 overflow created by the sum itself); every
+        reduce-scatter must then finish before the first update."""
         c = self.client
         if c.world_size == 1:
             return self.step()
+        if self._offload is not None:
+            raise NotImplementedError("step_with_collectives with offloaded chunks: run the "
+                                      "collectives yourself and call step()")
+        if scan not in ("local", "reduced"):
+            raise ValueError("scan must be 'local' or 'reduced'")
         lay = c.layout
         n_groups = lay.n_groups_comm
+        item = CHUNK_DESC_DTYPE.itemsize
         with torch.cuda.device(self.device):
             st = self._stream()
-            works = [c.reduce_scatter_group(g, async_op=True) for g in range(n_groups)]
-            item = CHUNK_DESC_DTYPE.itemsize
-            for g in range(n_groups):
-                works[g].wait()  # stream-level wait, not a host block
+            if scan == "local":
                 if self._dynamic:
-                    check(lib.ps_overflow_scan(self._desc_dev.data_ptr() + g * item, 1, self._max_numel,
-                                               self._scaler.flag_ptr, st), "ps_overflow_scan")
-            if self._dynamic:
-                c.all_reduce_flag(self._scaler.flag_tensor)
-            self._begin(c.world_size, st)
-            if self._offload is not None:
-                raise NotImplementedError("step_with_collectives with offloaded chunks: use step()")
-            works = []
+                    check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(),
+                                                      self._scaler.flag_ptr, st), "ps_overflow_scan_buffer")
+                    c.all_reduce_flag(self._scaler.flag_tensor)
+                self._begin(c.world_size, st)
+            rs = [c.reduce_scatter_group(g, async_op=True) for g in range(n_groups)]
+            if scan == "reduced":
+                for g in range(n_groups):
+                    rs[g].wait()  # stream-level wait, not a host block
+                    if self._dynamic:
+                        check(lib.ps_overflow_scan(self._desc_dev.data_ptr() + g * item, 1, self._max_numel,
+                                                   self._scaler.flag_ptr, st), "ps_overflow_scan")
+                if self._dynamic:
+                    c.all_reduce_flag(self._scaler.flag_tensor)
+                self._begin(c.world_size, st)
+            ag = []
             for g in range(n_groups):
+                if scan == "local":
+                    rs[g].wait()
                 self._update_resident(st, first=g, count=1)
-                works.append(c.all_gather_group(g, async_op=True))
-            for w in works:
+                ag.append(c.all_gather_group(g, async_op=True))
+            for w in ag:
                 w.wait()
         return None
 

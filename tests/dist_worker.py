@@ -12,6 +12,9 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
+SCAN = os.environ.get("PS_TEST_SCAN", "local")
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -75,7 +78,7 @@ def main():
                 tol = torch.maximum(want.abs() * 2.0 ** -10, torch.full_like(want, 2.0 ** -24))
                 assert ((got.double() - want).abs() <= tol).all(), "reduce-scatter off by more than 1 ulp"
             H.append(got.cpu().numpy().copy())
-        opt.step_with_collectives()
+        opt.step_with_collectives(scan=SCAN)
         skipped = orc.step(H, P, M, V, overflow=poisoned)
         assert skipped == poisoned
         torch.cuda.synchronize()

@@ -12,11 +12,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+@pytest.mark.parametrize("scan", ["local", "reduced"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_chunk_step_with_collectives(world):
+def test_chunk_step_with_collectives(world, scan):
     if torch.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PS_TEST_SCAN=scan)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world),
            os.path.join(ROOT, "tests", "dist_worker.py")]
