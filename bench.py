@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--scan", default="local", choices=["local", "reduced"],
                     help="N > 1: overflow test on local gradients before the reduction (the reference's "
                          "rule) or on the reduced ones")
+    ap.add_argument("--collectives", default="nccl", choices=["nccl", "fused"],
+                    help="N > 1: NCCL reduce-scatter / all-gather around the step kernel, or the one-kernel "
+                         "form over NVSwitch multicast memory")
     return ap.parse_args()
 
 
@@ -280,7 +283,9 @@ def run_ours(args):
         _lib.tune("blocks_per_sm", args.blocks_per_sm)
 
     cs, npr = args.chunk_size, args.chunks
-    client = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat")
+    fused = world > 1 and args.collectives == "fused"
+    client = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
+                         symmetric=fused)
     client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
     client.allocate()
     scaler = DynamicLossScaler(device=dev, **SCALER)
@@ -305,7 +310,9 @@ def run_ours(args):
             client.fp16_group(g).copy_(pristine)
 
     def one_step():
-        if world > 1:
+        if fused:
+            opt.step_fused_collectives()
+        elif world > 1:
             opt.step_with_collectives(scan=args.scan)
         else:
             opt.step()
@@ -314,6 +321,10 @@ def run_ours(args):
 
     def timed_kernel_step():
         """opt.step() with CUDA events around the fused chunk-step launch."""
+        if fused:
+            # the fused kernel is timed by the step itself (its launch is not a separate method)
+            one_step()
+            return
         orig = opt._update_resident
 
         def wrapped(st, first=0, count=None):
@@ -366,16 +377,28 @@ def run_ours(args):
     params_per_step = npr * cs * world
     value = params_per_step * args.steps / (total_ms * 1e-3)
 
-    kern_ms = [a.elapsed_time(b) for a, b, _ in kernel_ev]
-    kern_chunks = sum(c for _, _, c in kernel_ev)
-    kern_avg_ms = sum(kern_ms) / len(kern_ms)
     peak, peak_kind = measured_peaks()
-    bytes_per_launch = BYTES_PER_PARAM * cs * (kern_chunks / len(kernel_ev))
-    achieved = bytes_per_launch / (kern_avg_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "chunk_step_kernel", "achieved": achieved, "peak": peak,
-                "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
-                "traffic": None, "algorithmic_bytes_per_launch": bytes_per_launch,
-                "launch_ms": kern_avg_ms, "launches_timed": len(kernel_ev)}
+    if fused:
+        # NVLink-bound: per owned parameter 2 B x (world-1) leave every GPU for the in-switch
+        # reduction and 2 B x (world-1) arrive with the multicast store; measured peer-copy
+        # bandwidth on this pool is 770 GB/s per direction
+        link_bytes = 2 * (world - 1) * npr * cs
+        step_s = total_ms / args.steps * 1e-3
+        roofline = {"bound": "nvlink", "kernel": "chunk_step_fused_kernel", "achieved": link_bytes / step_s / 1e9,
+                    "peak": 770.0, "unit": "GB/s", "frac": link_bytes / step_s / 1e9 / 770.0,
+                    "peak_source": "measured peer copy per direction (whole step time, scan and barriers included)",
+                    "traffic": None, "algorithmic_bytes_per_launch": link_bytes, "launch_ms": None,
+                    "launches_timed": args.steps}
+    else:
+        kern_ms = [a.elapsed_time(b) for a, b, _ in kernel_ev]
+        kern_chunks = sum(c for _, _, c in kernel_ev)
+        kern_avg_ms = sum(kern_ms) / len(kern_ms)
+        bytes_per_launch = BYTES_PER_PARAM * cs * (kern_chunks / len(kernel_ev))
+        achieved = bytes_per_launch / (kern_avg_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "chunk_step_kernel", "achieved": achieved, "peak": peak,
+                    "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
+                    "traffic": None, "algorithmic_bytes_per_launch": bytes_per_launch,
+                    "launch_ms": kern_avg_ms, "launches_timed": len(kernel_ev)}
 
     local_step = None
     if world > 1:
@@ -399,7 +422,7 @@ def run_ours(args):
 
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(args, client, opt, pristine, world, rank, dev)
+        e2e = run_e2e(args, client, opt, pristine, world, rank, dev, one_step)
 
     if rank == 0:
         line = {
@@ -416,7 +439,9 @@ def run_ours(args):
             line["e2e"] = e2e
         if local_step is not None:
             line["local_step"] = local_step
-            line["config"]["overflow_scan"] = args.scan
+            line["config"]["overflow_scan"] = "local" if fused else args.scan
+            line["config"]["collectives"] = ("fused into the step kernel (multimem ld_reduce / st over NVSwitch)"
+                                             if fused else line["config"]["collectives"])
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cs)
         print(json.dumps(line))
@@ -424,7 +449,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_e2e(args, client, opt, pristine, world, rank, dev):
+def run_e2e(args, client, opt, pristine, world, rank, dev, one_step_fn):
     """The same step through the public API with HOST buffers: every step copies
     the rank's fp16 grads from pinned host memory into the fp16 slots, runs the
     step, and copies the updated fp16 params of the local chunks plus the
@@ -449,10 +474,7 @@ def run_e2e(args, client, opt, pristine, world, rank, dev):
                 evs.append(e)
         for e in evs:
             main.wait_event(e)
-        if world > 1:
-            opt.step_with_collectives(scan=args.scan)
-        else:
-            opt.step()
+        one_step_fn()
         done = torch.cuda.Event()
         done.record(main)
         with torch.cuda.stream(copy_out):

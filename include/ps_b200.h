@@ -229,6 +229,33 @@ int ps_scaler_update(ps_scaler_state* scaler_dev, int32_t* flag_dev, int overflo
 int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
                   const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, void* stream);
 
+/* The multi-GPU chunk step as ONE kernel: the step of ps_chunk_step fused with
+ * the reduce-scatter of the fp16 grad chunks before it
+ * (patrickstar/core/client.py:818-856) and the all-gather of the fp16 param
+ * chunks after it (client.py:428-497), over NVSwitch multicast memory.  Every
+ * rank holds the whole fp16 chunk list in a buffer that is mapped into one
+ * multicast object (same offset on every rank): fp16_local_base is this rank's
+ * buffer, fp16_multicast_base the multicast mapping of it.  The chunk table
+ * holds this rank's OWN chunks with h16 pointing into the local buffer.  For
+ * each owned element the gradient is loaded as the switch-side sum over all
+ * ranks' buffers (fp32 accumulation, one rounding to fp16) and the updated fp16
+ * param is stored to all ranks' buffers (single elements at ragged ends and
+ * segment boundaries go through peer_bases_dev, a device array of every rank's
+ * buffer base, because there is no 16-bit multicast access).  ctrl's slots must carry
+ * grad_divisor = world size (client.py:838).  The caller guarantees, with a
+ * barrier across ranks on each side, that every rank's gradients are complete
+ * before any rank launches and that no rank reads params or writes new
+ * gradients before every rank's launch has finished. */
+int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                        const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev,
+                        const void* fp16_local_base, const void* fp16_multicast_base,
+                        const uint64_t* peer_bases_dev, int world_size, void* stream);
+
+/* dst[i] = switch-side sum over all ranks of the fp16 value at multicast
+ * address fp16_multicast_ptr + 2*i — exactly what ps_chunk_step_fused loads as
+ * the reduced gradient (n even, 16-byte aligned pointers).  For tests. */
+int ps_multimem_reduce_probe(const void* fp16_multicast_ptr, uint16_t* dst_dev, size_t n, void* stream);
+
 /* Copies the device scaler state / control block to the host.  Synchronises
  * `stream`.  (DynamicLossScaler.loss_scale, state["step"].) */
 int ps_scaler_read(const ps_scaler_state* scaler_dev, ps_scaler_state* out_host, void* stream);

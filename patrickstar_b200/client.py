@@ -29,10 +29,15 @@ from .chunk_list import ChunkLayout, DEFAULT_CHUNK_SIZE
 
 class ChunkClient:
     def __init__(self, rank=0, default_chunk_size=DEFAULT_CHUNK_SIZE, config=None, world_size=None,
-                 device=None, pack="no_split", process_group=None):
+                 device=None, pack="no_split", process_group=None, symmetric=False):
         if not torch.cuda.is_available():
             raise RuntimeError("patrickstar_b200 needs a CUDA device (sm_100a); none found")
         self.local_rank = rank
+        # symmetric=True: the fp16 chunk buffer is allocated as NVSwitch multicast
+        # ("symmetric") memory, which the fused reduce-scatter + step + all-gather
+        # kernel needs; plain device memory otherwise
+        self.symmetric = bool(symmetric)
+        self.symm_handle = None
         if world_size is None:
             world_size = (torch.distributed.get_world_size(process_group)
                           if torch.distributed.is_available() and torch.distributed.is_initialized() else 1)
@@ -99,7 +104,19 @@ class ChunkClient:
             self.n_resident = max(0, min(n_local, int(state_budget_bytes) // per_chunk))
         n_off = n_local - self.n_resident
         dev = self.device
-        self.fp16 = torch.zeros(lay.n_chunks * cs, dtype=torch.float16, device=dev)
+        if self.symmetric and self.world_size > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = self.process_group if self.process_group is not None else torch.distributed.group.WORLD
+            self.fp16 = symm_mem.empty(lay.n_chunks * cs, dtype=torch.float16, device=dev)
+            self.fp16.zero_()
+            self.symm_handle = symm_mem.rendezvous(self.fp16, group)
+            self.fp16_multicast_ptr = int(self.symm_handle.multicast_ptr)
+            if self.fp16_multicast_ptr == 0:
+                raise RuntimeError("NVSwitch multicast is not available for this group of GPUs")
+            self.peer_bases = torch.tensor([int(p) for p in self.symm_handle.buffer_ptrs],
+                                           dtype=torch.int64, device=dev)
+        else:
+            self.fp16 = torch.zeros(lay.n_chunks * cs, dtype=torch.float16, device=dev)
 
         def dev_buf():
             return torch.zeros(max(self.n_resident, 0) * cs, dtype=torch.float32, device=dev)

@@ -179,6 +179,54 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p);
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 
+// NVSwitch multicast ("multimem") accesses on an address of the fp16 chunk
+// buffer's multicast mapping: the load returns the SUM over every rank's copy
+// (added in the switch, accumulated in fp32, rounded once to fp16), the store
+// writes every rank's copy.  They fuse the reduce-scatter of the gradient
+// chunks and the all-gather of the param chunks into the step kernel.
+__device__ __forceinline__ uint4 mm_ld_reduce_f16x8(const void* mc)
+{
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(mc)
+                 : "memory");
+    return r;
+}
+__device__ __forceinline__ void mm_st_f16x8(void* mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+                 "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// One element: there is no 16-bit multimem access, so a single gradient is taken
+// out of the reduced f16x2 pair that holds it (the two lanes are summed
+// independently), and a single fp16 param is stored to every rank's buffer with
+// plain peer stores.
+struct McCtx {
+    long long mc_delta;                 // multicast mapping minus local fp16 buffer, in bytes
+    const unsigned long long* peers;    // every rank's fp16 buffer base (device array)
+    const char* local_base;             // this rank's fp16 buffer base
+    int world;
+};
+__device__ __forceinline__ uint32_t mm_ld_reduce_f16(const uint16_t* local_elem, const McCtx& mc)
+{
+    const uintptr_t a = reinterpret_cast<uintptr_t>(local_elem);
+    const char* pair = reinterpret_cast<const char*>(a & ~(uintptr_t)3) + mc.mc_delta;
+    uint32_t r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.f16x2 %0, [%1];"
+                 : "=r"(r)
+                 : "l"(pair)
+                 : "memory");
+    return (a & 2) ? (r >> 16) : (r & 0xffffu);
+}
+__device__ __forceinline__ void peers_st_f16(uint16_t* local_elem, uint32_t h, const McCtx& mc)
+{
+    const long long off = reinterpret_cast<const char*>(local_elem) - mc.local_base;
+    for (int r = 0; r < mc.world; ++r)
+        *reinterpret_cast<uint16_t*>(mc.peers[r] + off) = (uint16_t)h;
+}
+
 // Index (absolute, in the segment table) of the last segment of [lo, hi) whose
 // start is <= e; lo when none starts at or before e.
 __device__ __forceinline__ uint32_t find_segment(const ps_segment* segs, uint32_t lo, uint32_t hi,
@@ -207,11 +255,11 @@ __device__ __forceinline__ SegView load_segment(const ps_segment* segs, uint32_t
 // Element-wise path for a group of up to 8 elements that is ragged (chunk end)
 // or straddles a segment boundary.  Scalar loads and stores; every element
 // looks up its own segment.
-template <bool kRestore, bool kGradHalf>
+template <bool kRestore, bool kGradHalf, bool kMC = false>
 __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads,
                                         const ps_segment* segs, uint32_t seg_lo, uint32_t seg_hi,
                                         const ps_hyper_slot* slots, uint32_t e, uint32_t e_end,
-                                        uint32_t si, uint16_t* p16_out)
+                                        uint32_t si, uint16_t* p16_out, McCtx mc = McCtx())
 {
     for (uint32_t i = e; i < e_end; ++i) {
         SegView sv = load_segment(segs, si);
@@ -222,12 +270,17 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         if (i < sv.start || i >= sv.end) continue;
         float p = d.p32[i];
         if (kRestore) {
-            if (p16_out) p16_out[i] = (uint16_t)float_to_half_bits(p);
+            if (kMC)
+                peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
+            else if (p16_out)
+                p16_out[i] = (uint16_t)float_to_half_bits(p);
             continue;
         }
         Slot s = load_slot(slots + sv.slot);
         float g;
-        if (kGradHalf)
+        if (kMC)
+            g = grad_from_half(mm_ld_reduce_f16(reinterpret_cast<const uint16_t*>(grads) + i, mc), s);
+        else if (kGradHalf)
             g = grad_from_half(reinterpret_cast<const uint16_t*>(grads)[i], s);
         else
             g = reinterpret_cast<const float*>(grads)[i];
@@ -236,7 +289,10 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         d.p32[i] = p;
         d.exp_avg[i] = m;
         d.exp_avg_sq[i] = v;
-        if (p16_out) p16_out[i] = (uint16_t)float_to_half_bits(p);
+        if (kMC)
+            peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
+        else if (p16_out)
+            p16_out[i] = (uint16_t)float_to_half_bits(p);
     }
 }
 
@@ -244,9 +300,10 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
 // at tile_base + (j * kThreads + t) * 8, so that every warp-wide access is one
 // contiguous 512-byte (fp16) or 2 x 512-byte (fp32) run.  All loads of the tile
 // are issued before the first dependent instruction.
-template <int U, bool kRestore, bool kWrite16>
+template <int U, bool kRestore, bool kWrite16, bool kMC = false>
 __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segment* segs,
-                                          const ps_hyper_slot* slots, uint32_t tile_base)
+                                          const ps_hyper_slot* slots, uint32_t tile_base,
+                                          McCtx mc = McCtx())
 {
     uint4 gq[U];
     float4 pq[U][2], mq[U][2], vq[U][2];
@@ -261,7 +318,10 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
             pq[j][0] = ld_stream(pp);
             pq[j][1] = ld_stream(pp + 1);
             if (!kRestore) {
-                gq[j] = ld_stream(reinterpret_cast<const uint4*>(d.h16 + e[j]));
+                if (kMC)
+                    gq[j] = mm_ld_reduce_f16x8(reinterpret_cast<const char*>(d.h16 + e[j]) + mc.mc_delta);
+                else
+                    gq[j] = ld_stream(reinterpret_cast<const uint4*>(d.h16 + e[j]));
                 const float4* mp = reinterpret_cast<const float4*>(d.exp_avg + e[j]);
                 const float4* vp = reinterpret_cast<const float4*>(d.exp_avg_sq + e[j]);
                 mq[j][0] = ld_stream(mp);
@@ -279,8 +339,8 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
         SegView sv = load_segment(segs, si);
         if (!(full[j] && sv.start <= e[j] && e[j] + kVec <= sv.end)) {
             uint32_t e_end = e[j] + kVec < d.numel ? e[j] + kVec : d.numel;
-            slow_group<kRestore, true>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e[j], e_end,
-                                       si, kWrite16 ? d.h16 : nullptr);
+            slow_group<kRestore, true, kMC>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e[j], e_end,
+                                            si, kWrite16 ? d.h16 : nullptr, mc);
             continue;
         }
         float p[8] = {pq[j][0].x, pq[j][0].y, pq[j][0].z, pq[j][0].w,
@@ -313,7 +373,10 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
         out.y = float_to_half_bits(p[2]) | (float_to_half_bits(p[3]) << 16);
         out.z = float_to_half_bits(p[4]) | (float_to_half_bits(p[5]) << 16);
         out.w = float_to_half_bits(p[6]) | (float_to_half_bits(p[7]) << 16);
-        st_stream(reinterpret_cast<uint4*>(d.h16 + e[j]), out);
+        if (kMC)
+            mm_st_f16x8(reinterpret_cast<char*>(d.h16 + e[j]) + mc.mc_delta, out);
+        else
+            st_stream(reinterpret_cast<uint4*>(d.h16 + e[j]), out);
     }
 }
 
@@ -356,6 +419,60 @@ chunk_step_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
         else
             step_tile<U, false, true>(d, segs, slots, tile_base);
     }
+}
+
+// The chunk step fused with its two collectives (multi-GPU): the gradient of an
+// element is the switch-side sum over all ranks' fp16 buffers (the
+// reduce-scatter), the updated fp16 param is stored to all ranks' buffers (the
+// all-gather).  `mc_delta` is the byte distance from this rank's fp16 buffer to
+// its multicast mapping.  Every element is read and then written by the one
+// thread that owns it, on the one rank that owns its chunk, so no rank-to-rank
+// ordering is needed inside the kernel; the caller brackets the launch with
+// barriers across ranks (gradients complete before, params visible after).
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                        uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
+                        const ps_step_ctrl* __restrict__ ctrl, McCtx mc)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    const int skip = __ldg(&ctrl->skip);
+    const ps_hyper_slot* slots = ctrl->slots;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+        const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+        const ps_chunk_desc d = load_desc(chunks + c);
+        const uint32_t tile_base = lt * kTile;
+        if (tile_base >= d.numel) continue;
+        if (skip)
+            step_tile<U, true, true, true>(d, segs, slots, tile_base, mc);
+        else
+            step_tile<U, false, true, true>(d, segs, slots, tile_base, mc);
+    }
+    // the params stored to the other ranks are ordered before the end of the kernel
+    __threadfence_system();
+}
+
+// dst[i] = sum over ranks of their fp16 buffers at the multicast address mc[i]
+// (what the fused kernel's gradient load returns); for tests.
+__global__ void __launch_bounds__(kThreads)
+multimem_reduce_probe_kernel(const uint16_t* mc, uint16_t* dst, size_t n)
+{
+    const size_t n_vec = n / kVec;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec;
+         i += (size_t)gridDim.x * kThreads)
+        reinterpret_cast<uint4*>(dst)[i] = mm_ld_reduce_f16x8(mc + i * kVec);
+    if (blockIdx.x == 0)
+        for (size_t i = n_vec * kVec + threadIdx.x; i < n; i += kThreads)
+        {
+            McCtx ctx;
+            ctx.mc_delta = 0;  // `mc` already is the multicast address
+            ctx.peers = nullptr;
+            ctx.local_base = nullptr;
+            ctx.world = 0;
+            dst[i] = (uint16_t)mm_ld_reduce_f16(mc + i, ctx);
+        }
 }
 
 // Tensor-level variant (image of adam_update): `d` holds the four pointers
@@ -768,6 +885,21 @@ int launch_chunk_step(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t m
     return after_launch();
 }
 
+template <int U>
+int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
+                            const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc,
+                            cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    uint64_t total = (uint64_t)tpc * n_chunks;
+    int grid = 1;
+    int rc = grid_for(chunk_step_fused_kernel<U>, total, &grid, 2);
+    if (rc != PS_OK) return rc;
+    chunk_step_fused_kernel<U><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    return after_launch();
+}
+
 template <int U, bool kWrite16>
 int launch_tensor_step(const ps_chunk_desc& d, uint32_t head, const ps_hyper_slot& slot,
                        cudaStream_t st)
@@ -1123,6 +1255,49 @@ int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t m
         case 4: return launch_chunk_step<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
         default: return launch_chunk_step<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
     }
+}
+
+int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                        const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev,
+                        const void* fp16_local_base, const void* fp16_multicast_base,
+                        const uint64_t* peer_bases_dev, int world_size, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_dev == nullptr || segs_dev == nullptr || ctrl_dev == nullptr ||
+        fp16_local_base == nullptr || fp16_multicast_base == nullptr || peer_bases_dev == nullptr)
+        return PS_ERR_INVALID;
+    if (world_size < 2 || world_size > 64) return PS_ERR_INVALID;
+    if (((uintptr_t)fp16_local_base | (uintptr_t)fp16_multicast_base) & 15u) return PS_ERR_ALIGN;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    McCtx mc;
+    mc.mc_delta = (long long)((intptr_t)fp16_multicast_base - (intptr_t)fp16_local_base);
+    mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
+    mc.world = world_size;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (g_tune.unroll) {
+        case 1: return launch_chunk_step_fused<1>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 4: return launch_chunk_step_fused<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        default: return launch_chunk_step_fused<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    }
+}
+
+int ps_multimem_reduce_probe(const void* fp16_multicast_ptr, uint16_t* dst_dev, size_t n, void* stream)
+{
+    if (n == 0) return PS_OK;
+    if (fp16_multicast_ptr == nullptr || dst_dev == nullptr) return PS_ERR_INVALID;
+    if (((uintptr_t)fp16_multicast_ptr | (uintptr_t)dst_dev) & 15u) return PS_ERR_ALIGN;
+    if (n & 1u) return PS_ERR_INVALID;  // the reduced loads work on fp16 pairs
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    uint64_t blocks = (n / kVec + kThreads - 1) / kThreads;
+    uint64_t cap = (uint64_t)di.sm_count * 8u;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (grid < 1) grid = 1;
+    multimem_reduce_probe_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint16_t*>(fp16_multicast_ptr), dst_dev, n);
+    return after_launch();
 }
 
 int ps_scaler_read(const ps_scaler_state* scaler_dev, ps_scaler_state* out_host, void* stream)

@@ -282,6 +282,58 @@ class FP16Adam(torch.optim.Optimizer):
                 w.wait()
         return None
 
+    @torch.no_grad()
+    def step_fused_collectives(self):
+        """The multi-GPU chunk step as ONE kernel over NVSwitch multicast memory
+        (needs ``ChunkClient(symmetric=True)``): the gradient of every owned
+        element is loaded as the in-switch sum over all ranks' fp16 buffers — the
+        reduce-scatter of patrickstar/core/client.py:818-856 — and the updated
+        fp16 param is stored to all ranks' buffers — the all-gather of
+        client.py:428-497.  Nothing crosses NVLink twice and no collective kernel
+        runs beside the step.
+
+        Order on every rank: overflow scan of the rank's own gradients (the
+        reference's pre-reduction check, patrickstar/core/hook.py:212), MAX
+        all-reduce of the flag (which is also the barrier "all gradients are
+        written"), step-begin, the fused kernel over the owned chunks, a 4-byte
+        all-reduce as the barrier "all params have arrived"."""
+        c = self.client
+        if c.world_size == 1:
+            return self.step()
+        if c.symm_handle is None:
+            raise RuntimeError("step_fused_collectives needs ChunkClient(symmetric=True)")
+        if self._offload is not None:
+            raise NotImplementedError("fused collectives with offloaded chunks")
+        with torch.cuda.device(self.device):
+            st = self._stream()
+            if self._dynamic:
+                check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(), self._scaler.flag_ptr, st),
+                      "ps_overflow_scan_buffer")
+            c.all_reduce_flag(self._scaler.flag_tensor)
+            self._begin(c.world_size, st)
+            check(lib.ps_chunk_step_fused(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
+                                          self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
+                                          c.fp16_multicast_ptr, c.peer_bases.data_ptr(), c.world_size, st),
+                  "ps_chunk_step_fused")
+            if getattr(self, "_barrier_buf", None) is None:
+                self._barrier_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
+            c.all_reduce_flag(self._barrier_buf)
+        return None
+
+    def reduced_gradients(self):
+        """What the fused kernel loads as gradients: per owned chunk the in-switch
+        sum of all ranks' fp16 slots (for tests; call between two barriers)."""
+        c = self.client
+        cs = c.layout.chunk_size
+        out = []
+        with torch.cuda.device(self.device):
+            for cid in c.local_ids:
+                dst = torch.empty(cs, dtype=torch.float16, device=self.device)
+                check(lib.ps_multimem_reduce_probe(c.fp16_multicast_ptr + 2 * cid * cs, dst.data_ptr(), cs,
+                                                   self._stream()), "ps_multimem_reduce_probe")
+                out.append(dst)
+        return out
+
     # --------------------------------------------------------------- inspection
     def read_ctrl(self) -> StepCtrl:
         out = StepCtrl()
