@@ -50,9 +50,11 @@ def parse_args():
     ap.add_argument("--scan", default="local", choices=["local", "reduced"],
                     help="N > 1: overflow test on local gradients before the reduction (the reference's "
                          "rule) or on the reduced ones")
-    ap.add_argument("--collectives", default="nccl", choices=["nccl", "fused"],
-                    help="N > 1: NCCL reduce-scatter / all-gather around the step kernel, or the one-kernel "
-                         "form over NVSwitch multicast memory")
+    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "fused", "p2p"],
+                    help="N > 1: 'nccl' = NCCL reduce-scatter / all-gather pipelined around the step kernel; "
+                         "'fused' = one kernel over NVSwitch multicast memory (multimem); 'p2p' = one kernel "
+                         "over peer loads / stores; 'auto' = p2p for 2-3 ranks, fused for more, nccl if "
+                         "symmetric memory cannot be set up")
     return ap.parse_args()
 
 
@@ -283,11 +285,35 @@ def run_ours(args):
         _lib.tune("blocks_per_sm", args.blocks_per_sm)
 
     cs, npr = args.chunk_size, args.chunks
-    fused = world > 1 and args.collectives == "fused"
-    client = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
-                         symmetric=fused)
-    client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
-    client.allocate()
+    if args.collectives == "auto":
+        args.collectives = "nccl" if world == 1 else ("p2p" if world <= 3 else "fused")
+    fused = world > 1 and args.collectives in ("fused", "p2p")
+
+    def make_client(symmetric):
+        c = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
+                        symmetric=symmetric)
+        c.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
+        c.allocate()
+        return c
+
+    fallback_note = None
+    if fused:
+        # every rank must take the same path: agree on whether symmetric memory came up
+        try:
+            client = make_client(True)
+            ok = 1
+        except Exception as e:  # noqa: BLE001 - any set-up failure means "use NCCL"
+            client, ok, fallback_note = None, 0, "symmetric memory unavailable (%s): NCCL collectives" % type(e).__name__
+        t = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if int(t.item()) == 0:
+            fused, args.collectives = False, "nccl"
+            fallback_note = fallback_note or "symmetric memory unavailable on another rank: NCCL collectives"
+            del client
+            torch.cuda.empty_cache()
+            client = make_client(False)
+    else:
+        client = make_client(False)
     scaler = DynamicLossScaler(device=dev, **SCALER)
     opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
 
@@ -311,7 +337,7 @@ def run_ours(args):
 
     def one_step():
         if fused:
-            opt.step_fused_collectives()
+            opt.step_fused_collectives("multimem" if args.collectives == "fused" else "p2p")
         elif world > 1:
             opt.step_with_collectives(scan=args.scan)
         else:
@@ -384,7 +410,7 @@ def run_ours(args):
         # bandwidth on this pool is 770 GB/s per direction
         link_bytes = 2 * (world - 1) * npr * cs
         step_s = total_ms / args.steps * 1e-3
-        roofline = {"bound": "nvlink", "kernel": "chunk_step_fused_kernel", "achieved": link_bytes / step_s / 1e9,
+        roofline = {"bound": "nvlink", "kernel": "chunk_step_fused_kernel" if args.collectives == "fused" else "chunk_step_p2p_kernel", "achieved": link_bytes / step_s / 1e9,
                     "peak": 770.0, "unit": "GB/s", "frac": link_bytes / step_s / 1e9 / 770.0,
                     "peak_source": "measured peer copy per direction (whole step time, scan and barriers included)",
                     "traffic": None, "algorithmic_bytes_per_launch": link_bytes, "launch_ms": None,
@@ -437,10 +463,13 @@ def run_ours(args):
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if fallback_note:
+            line["config"]["note"] = fallback_note
         if local_step is not None:
             line["local_step"] = local_step
             line["config"]["overflow_scan"] = "local" if fused else args.scan
-            line["config"]["collectives"] = ("fused into the step kernel (multimem ld_reduce / st over NVSwitch)"
+            line["config"]["collectives"] = (("fused into the step kernel (multimem ld_reduce / st over NVSwitch)" if args.collectives == "fused"
+                                              else "fused into the step kernel (peer loads / stores over NVLink)")
                                              if fused else line["config"]["collectives"])
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cs)

@@ -251,6 +251,20 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
                         const void* fp16_local_base, const void* fp16_multicast_base,
                         const uint64_t* peer_bases_dev, int world_size, void* stream);
 
+/* The same fusion over plain peer mappings (no multicast object): the gradient
+ * of an owned element is the sum of the world_size ranks' values read through
+ * peer_bases_dev, accumulated in fp32 in rank order and rounded once to fp16;
+ * the updated fp16 param is stored into every rank's buffer.  world_size <= 8.
+ * Same barriers as ps_chunk_step_fused. */
+int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                      const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, const void* fp16_local_base,
+                      const uint64_t* peer_bases_dev, int world_size, void* stream);
+
+/* dst[i] = the reduced gradient ps_chunk_step_p2p loads for the element at
+ * fp16_local_ptr + 2*i of this rank's buffer.  For tests. */
+int ps_p2p_reduce_probe(const void* fp16_local_ptr, const void* fp16_local_base, const uint64_t* peer_bases_dev,
+                        int world_size, uint16_t* dst_dev, size_t n, void* stream);
+
 /* dst[i] = switch-side sum over all ranks of the fp16 value at multicast
  * address fp16_multicast_ptr + 2*i — exactly what ps_chunk_step_fused loads as
  * the reduced gradient (n even, 16-byte aligned pointers).  For tests. */

@@ -112,6 +112,8 @@ SIGNATURES = {
     "ps_offload_step": (C.c_int, [_p, _p, C.c_uint32, _p, _p, _p, _p, _p]),
     "ps_offload_last_cuda_error": (C.c_int, []),
     "ps_chunk_step_fused": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, _p, C.c_int, _p]),
+    "ps_chunk_step_p2p": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, C.c_int, _p]),
+    "ps_p2p_reduce_probe": (C.c_int, [_p, _p, _p, C.c_int, _p, C.c_size_t, _p]),
     "ps_multimem_reduce_probe": (C.c_int, [_p, _p, C.c_size_t, _p]),
     "ps_scaler_read": (C.c_int, [_p, C.POINTER(ScalerState), _p]),
     "ps_ctrl_read": (C.c_int, [_p, C.POINTER(StepCtrl), _p]),

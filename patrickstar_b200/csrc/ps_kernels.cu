@@ -227,6 +227,62 @@ __device__ __forceinline__ void peers_st_f16(uint16_t* local_elem, uint32_t h, c
         *reinterpret_cast<uint16_t*>(mc.peers[r] + off) = (uint16_t)h;
 }
 
+// Peer-to-peer form of the same fusion, over plain peer mappings of every
+// rank's fp16 buffer: the gradient of an element is the sum of the W ranks'
+// values, accumulated in fp32 in rank order and rounded once to fp16; the
+// updated param is stored into every rank's buffer.
+constexpr int kMaxPeers = 8;
+// kColl values of the step templates: 0 no collective, 1 multimem, 2 / 24 / 22
+// peer-to-peer compiled for up to 8 / 4 / 2 ranks (fewer ranks, fewer registers)
+__host__ __device__ constexpr int peers_of(int kColl) { return kColl == 22 ? 2 : (kColl == 24 ? 4 : 8); }
+__host__ __device__ constexpr bool is_p2p(int kColl) { return kColl == 2 || kColl == 22 || kColl == 24; }
+
+template <int NP>
+__device__ __forceinline__ uint4 p2p_ld_reduce_f16x8(const uint16_t* local_vec, const McCtx& mc)
+{
+    const long long off = reinterpret_cast<const char*>(local_vec) - mc.local_base;
+    uint4 q[NP];
+#pragma unroll
+    for (int r = 0; r < NP; ++r)
+        if (r < mc.world) q[r] = *reinterpret_cast<const uint4*>(mc.peers[r] + off);
+    float acc[8];
+    uint32_t w0[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        acc[k] = half_bits_to_float((k & 1) ? (w0[k >> 1] >> 16) : (w0[k >> 1] & 0xffffu));
+#pragma unroll
+    for (int r = 1; r < NP; ++r) {
+        if (r < mc.world) {
+            uint32_t w[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                acc[k] = __fadd_rn(acc[k], half_bits_to_float((k & 1) ? (w[k >> 1] >> 16) : (w[k >> 1] & 0xffffu)));
+        }
+    }
+    uint4 out;
+    out.x = float_to_half_bits(acc[0]) | (float_to_half_bits(acc[1]) << 16);
+    out.y = float_to_half_bits(acc[2]) | (float_to_half_bits(acc[3]) << 16);
+    out.z = float_to_half_bits(acc[4]) | (float_to_half_bits(acc[5]) << 16);
+    out.w = float_to_half_bits(acc[6]) | (float_to_half_bits(acc[7]) << 16);
+    return out;
+}
+__device__ __forceinline__ uint32_t p2p_ld_reduce_f16(const uint16_t* local_elem, const McCtx& mc)
+{
+    const long long off = reinterpret_cast<const char*>(local_elem) - mc.local_base;
+    float acc = half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.peers[0] + off));
+    for (int r = 1; r < mc.world; ++r)
+        acc = __fadd_rn(acc, half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.peers[r] + off)));
+    return float_to_half_bits(acc);
+}
+template <int NP>
+__device__ __forceinline__ void p2p_st_f16x8(uint16_t* local_vec, uint4 v, const McCtx& mc)
+{
+    const long long off = reinterpret_cast<const char*>(local_vec) - mc.local_base;
+#pragma unroll
+    for (int r = 0; r < NP; ++r)
+        if (r < mc.world) *reinterpret_cast<uint4*>(mc.peers[r] + off) = v;
+}
+
 // Index (absolute, in the segment table) of the last segment of [lo, hi) whose
 // start is <= e; lo when none starts at or before e.
 __device__ __forceinline__ uint32_t find_segment(const ps_segment* segs, uint32_t lo, uint32_t hi,
@@ -255,7 +311,7 @@ __device__ __forceinline__ SegView load_segment(const ps_segment* segs, uint32_t
 // Element-wise path for a group of up to 8 elements that is ragged (chunk end)
 // or straddles a segment boundary.  Scalar loads and stores; every element
 // looks up its own segment.
-template <bool kRestore, bool kGradHalf, bool kMC = false>
+template <bool kRestore, bool kGradHalf, int kColl = 0>
 __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads,
                                         const ps_segment* segs, uint32_t seg_lo, uint32_t seg_hi,
                                         const ps_hyper_slot* slots, uint32_t e, uint32_t e_end,
@@ -270,7 +326,7 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         if (i < sv.start || i >= sv.end) continue;
         float p = d.p32[i];
         if (kRestore) {
-            if (kMC)
+            if (kColl)
                 peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
             else if (p16_out)
                 p16_out[i] = (uint16_t)float_to_half_bits(p);
@@ -278,8 +334,10 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         }
         Slot s = load_slot(slots + sv.slot);
         float g;
-        if (kMC)
+        if (kColl == 1)
             g = grad_from_half(mm_ld_reduce_f16(reinterpret_cast<const uint16_t*>(grads) + i, mc), s);
+        else if (is_p2p(kColl))
+            g = grad_from_half(p2p_ld_reduce_f16(reinterpret_cast<const uint16_t*>(grads) + i, mc), s);
         else if (kGradHalf)
             g = grad_from_half(reinterpret_cast<const uint16_t*>(grads)[i], s);
         else
@@ -289,7 +347,7 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         d.p32[i] = p;
         d.exp_avg[i] = m;
         d.exp_avg_sq[i] = v;
-        if (kMC)
+        if (kColl)
             peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
         else if (p16_out)
             p16_out[i] = (uint16_t)float_to_half_bits(p);
@@ -300,10 +358,10 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
 // at tile_base + (j * kThreads + t) * 8, so that every warp-wide access is one
 // contiguous 512-byte (fp16) or 2 x 512-byte (fp32) run.  All loads of the tile
 // are issued before the first dependent instruction.
-template <int U, bool kRestore, bool kWrite16, bool kMC = false>
+template <int U, bool kRestore, bool kWrite16, int kColl = 0, bool kPre = false>
 __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segment* segs,
                                           const ps_hyper_slot* slots, uint32_t tile_base,
-                                          McCtx mc = McCtx())
+                                          McCtx mc = McCtx(), const uint4* pre = nullptr)
 {
     uint4 gq[U];
     float4 pq[U][2], mq[U][2], vq[U][2];
@@ -318,8 +376,12 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
             pq[j][0] = ld_stream(pp);
             pq[j][1] = ld_stream(pp + 1);
             if (!kRestore) {
-                if (kMC)
+                if (kPre)
+                    gq[j] = pre[j];  // loaded by the caller some tiles ago
+                else if (kColl == 1)
                     gq[j] = mm_ld_reduce_f16x8(reinterpret_cast<const char*>(d.h16 + e[j]) + mc.mc_delta);
+                else if (is_p2p(kColl))
+                    gq[j] = p2p_ld_reduce_f16x8<peers_of(kColl)>(d.h16 + e[j], mc);
                 else
                     gq[j] = ld_stream(reinterpret_cast<const uint4*>(d.h16 + e[j]));
                 const float4* mp = reinterpret_cast<const float4*>(d.exp_avg + e[j]);
@@ -339,7 +401,7 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
         SegView sv = load_segment(segs, si);
         if (!(full[j] && sv.start <= e[j] && e[j] + kVec <= sv.end)) {
             uint32_t e_end = e[j] + kVec < d.numel ? e[j] + kVec : d.numel;
-            slow_group<kRestore, true, kMC>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e[j], e_end,
+            slow_group<kRestore, true, kColl>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e[j], e_end,
                                             si, kWrite16 ? d.h16 : nullptr, mc);
             continue;
         }
@@ -373,8 +435,10 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
         out.y = float_to_half_bits(p[2]) | (float_to_half_bits(p[3]) << 16);
         out.z = float_to_half_bits(p[4]) | (float_to_half_bits(p[5]) << 16);
         out.w = float_to_half_bits(p[6]) | (float_to_half_bits(p[7]) << 16);
-        if (kMC)
+        if (kColl == 1)
             mm_st_f16x8(reinterpret_cast<char*>(d.h16 + e[j]) + mc.mc_delta, out);
+        else if (is_p2p(kColl))
+            p2p_st_f16x8<peers_of(kColl)>(d.h16 + e[j], out, mc);
         else
             st_stream(reinterpret_cast<uint4*>(d.h16 + e[j]), out);
     }
@@ -429,11 +493,77 @@ chunk_step_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
 // thread that owns it, on the one rank that owns its chunk, so no rank-to-rank
 // ordering is needed inside the kernel; the caller brackets the launch with
 // barriers across ranks (gradients complete before, params visible after).
-template <int U>
+//
+// The kernel is bound by NVLink, whose round trip through the switch is several
+// times the HBM latency, so the reduced gradient loads run kFusedDepth tiles
+// ahead of the rest: a thread keeps that many 16-byte multimem loads in flight
+// in a register ring while it works on the current tile (one 8-element group
+// per thread and tile, to leave the registers to the ring).
+constexpr int kFusedDepth = 4;
+
+__device__ __forceinline__ uint4 fused_prefetch(const ps_chunk_desc* chunks, uint32_t tiles_per_chunk,
+                                                uint64_t t, uint64_t total, int skip, const McCtx& mc)
+{
+    uint4 g = make_uint4(0u, 0u, 0u, 0u);
+    if (skip || t >= total) return g;
+    const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+    const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+    const uint16_t* h16 = reinterpret_cast<const uint16_t*>(
+        __ldg(reinterpret_cast<const unsigned long long*>(&chunks[c].h16)));
+    const uint32_t numel = __ldg(&chunks[c].numel);
+    const uint32_t e = lt * (uint32_t)(kThreads * kVec) + threadIdx.x * kVec;
+    if (e + kVec <= numel) g = mm_ld_reduce_f16x8(reinterpret_cast<const char*>(h16 + e) + mc.mc_delta);
+    return g;
+}
+
 __global__ void __launch_bounds__(kThreads)
 chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
                         uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
                         const ps_step_ctrl* __restrict__ ctrl, McCtx mc)
+{
+    constexpr uint32_t kTile = kThreads * kVec;
+    const int skip = __ldg(&ctrl->skip);
+    const ps_hyper_slot* slots = ctrl->slots;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    const uint64_t stride = gridDim.x;
+    uint4 ring[kFusedDepth];
+#pragma unroll
+    for (int k = 0; k < kFusedDepth; ++k)
+        ring[k] = fused_prefetch(chunks, tiles_per_chunk, blockIdx.x + (uint64_t)k * stride, total, skip, mc);
+    uint64_t t = blockIdx.x;
+    while (t < total) {
+#pragma unroll
+        for (int k = 0; k < kFusedDepth; ++k) {
+            if (t < total) {
+                const uint4 g = ring[k];
+                ring[k] = fused_prefetch(chunks, tiles_per_chunk, t + (uint64_t)kFusedDepth * stride, total,
+                                         skip, mc);
+                const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+                const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+                const ps_chunk_desc d = load_desc(chunks + c);
+                const uint32_t tile_base = lt * kTile;
+                if (tile_base < d.numel) {
+                    if (skip)
+                        step_tile<1, true, true, 1, false>(d, segs, slots, tile_base, mc);
+                    else
+                        step_tile<1, false, true, 1, true>(d, segs, slots, tile_base, mc, &g);
+                }
+                t += stride;
+            }
+        }
+    }
+    // the params stored to the other ranks are ordered before the end of the kernel
+    __threadfence_system();
+}
+
+// Peer-to-peer form of the fused kernel (no multicast object needed; the sums are
+// exact fp32 accumulations).  Enough independent peer loads are in flight per
+// thread (W per 8-element group) that no register ring is needed.
+template <int U, int kColl>
+__global__ void __launch_bounds__(kThreads, 2)
+chunk_step_p2p_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                      uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
+                      const ps_step_ctrl* __restrict__ ctrl, McCtx mc)
 {
     constexpr uint32_t kTile = kThreads * kVec * U;
     const int skip = __ldg(&ctrl->skip);
@@ -446,12 +576,25 @@ chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chu
         const uint32_t tile_base = lt * kTile;
         if (tile_base >= d.numel) continue;
         if (skip)
-            step_tile<U, true, true, true>(d, segs, slots, tile_base, mc);
+            step_tile<U, true, true, kColl>(d, segs, slots, tile_base, mc);
         else
-            step_tile<U, false, true, true>(d, segs, slots, tile_base, mc);
+            step_tile<U, false, true, kColl>(d, segs, slots, tile_base, mc);
     }
-    // the params stored to the other ranks are ordered before the end of the kernel
     __threadfence_system();
+}
+
+// dst[i] = the peer-to-peer kernel's reduced gradient of the element at byte
+// offset 2*i from `local_ptr` in this rank's buffer; for tests.
+__global__ void __launch_bounds__(kThreads)
+p2p_reduce_probe_kernel(const uint16_t* local_ptr, uint16_t* dst, size_t n, McCtx mc)
+{
+    const size_t n_vec = n / kVec;
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec;
+         i += (size_t)gridDim.x * kThreads)
+        reinterpret_cast<uint4*>(dst)[i] = p2p_ld_reduce_f16x8<kMaxPeers>(local_ptr + i * kVec, mc);
+    if (blockIdx.x == 0)
+        for (size_t i = n_vec * kVec + threadIdx.x; i < n; i += kThreads)
+            dst[i] = (uint16_t)p2p_ld_reduce_f16(local_ptr + i, mc);
 }
 
 // dst[i] = sum over ranks of their fp16 buffers at the multicast address mc[i]
@@ -885,18 +1028,29 @@ int launch_chunk_step(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t m
     return after_launch();
 }
 
-template <int U>
 int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
-                            const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc,
-                            cudaStream_t st)
+                            const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
 {
-    constexpr uint32_t kTile = kThreads * kVec * U;
+    constexpr uint32_t kTile = kThreads * kVec;
     uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
     uint64_t total = (uint64_t)tpc * n_chunks;
     int grid = 1;
-    int rc = grid_for(chunk_step_fused_kernel<U>, total, &grid, 2);
+    int rc = grid_for(chunk_step_fused_kernel, total, &grid, 1);
     if (rc != PS_OK) return rc;
-    chunk_step_fused_kernel<U><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    chunk_step_fused_kernel<<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    return after_launch();
+}
+
+template <int U, int kColl>
+int launch_chunk_step_p2p(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
+                          const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    int grid = 1;
+    int rc = grid_for(chunk_step_p2p_kernel<U, kColl>, (uint64_t)tpc * n_chunks, &grid, 2);
+    if (rc != PS_OK) return rc;
+    chunk_step_p2p_kernel<U, kColl><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
     return after_launch();
 }
 
@@ -1274,12 +1428,61 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
+    return launch_chunk_step_fused(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc,
+                                   (cudaStream_t)stream);
+}
+
+int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                      const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, const void* fp16_local_base,
+                      const uint64_t* peer_bases_dev, int world_size, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_dev == nullptr || segs_dev == nullptr || ctrl_dev == nullptr || fp16_local_base == nullptr ||
+        peer_bases_dev == nullptr)
+        return PS_ERR_INVALID;
+    if (world_size < 2 || world_size > kMaxPeers) return PS_ERR_LIMIT;
+    if ((uintptr_t)fp16_local_base & 15u) return PS_ERR_ALIGN;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    McCtx mc;
+    mc.mc_delta = 0;
+    mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
+    mc.world = world_size;
     cudaStream_t st = (cudaStream_t)stream;
-    switch (g_tune.unroll) {
-        case 1: return launch_chunk_step_fused<1>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-        case 4: return launch_chunk_step_fused<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-        default: return launch_chunk_step_fused<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-    }
+    // few ranks: few peer loads per group, so two groups per thread keep the link busy
+    int rc;
+    if (world_size <= 2)
+        rc = launch_chunk_step_p2p<2, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 4)
+        rc = launch_chunk_step_p2p<1, 24>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else
+        rc = launch_chunk_step_p2p<1, 2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    return rc;
+}
+
+int ps_p2p_reduce_probe(const void* fp16_local_ptr, const void* fp16_local_base, const uint64_t* peer_bases_dev,
+                        int world_size, uint16_t* dst_dev, size_t n, void* stream)
+{
+    if (n == 0) return PS_OK;
+    if (fp16_local_ptr == nullptr || fp16_local_base == nullptr || peer_bases_dev == nullptr || dst_dev == nullptr)
+        return PS_ERR_INVALID;
+    if (world_size < 2 || world_size > kMaxPeers) return PS_ERR_LIMIT;
+    if (((uintptr_t)fp16_local_ptr | (uintptr_t)fp16_local_base | (uintptr_t)dst_dev) & 15u) return PS_ERR_ALIGN;
+    McCtx mc;
+    mc.mc_delta = 0;
+    mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
+    mc.world = world_size;
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    uint64_t blocks = (n / kVec + kThreads - 1) / kThreads;
+    uint64_t cap = (uint64_t)di.sm_count * 8u;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (grid < 1) grid = 1;
+    p2p_reduce_probe_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint16_t*>(fp16_local_ptr), dst_dev, n, mc);
+    return after_launch();
 }
 
 int ps_multimem_reduce_probe(const void* fp16_multicast_ptr, uint16_t* dst_dev, size_t n, void* stream)

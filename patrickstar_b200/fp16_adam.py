@@ -283,7 +283,7 @@ class FP16Adam(torch.optim.Optimizer):
         return None
 
     @torch.no_grad()
-    def step_fused_collectives(self):
+    def step_fused_collectives(self, transport="multimem"):
         """The multi-GPU chunk step as ONE kernel over NVSwitch multicast memory
         (needs ``ChunkClient(symmetric=True)``): the gradient of every owned
         element is loaded as the in-switch sum over all ranks' fp16 buffers — the
@@ -296,7 +296,12 @@ class FP16Adam(torch.optim.Optimizer):
         reference's pre-reduction check, patrickstar/core/hook.py:212), MAX
         all-reduce of the flag (which is also the barrier "all gradients are
         written"), step-begin, the fused kernel over the owned chunks, a 4-byte
-        all-reduce as the barrier "all params have arrived"."""
+        all-reduce as the barrier "all params have arrived".
+
+        ``transport="multimem"``: in-switch reduction and multicast stores;
+        ``transport="p2p"``: peer loads summed in fp32 in rank order and peer
+        stores (exact single rounding, no multicast object needed, cheaper on
+        the links for 2-3 ranks, dearer for 8)."""
         c = self.client
         if c.world_size == 1:
             return self.step()
@@ -311,26 +316,39 @@ class FP16Adam(torch.optim.Optimizer):
                       "ps_overflow_scan_buffer")
             c.all_reduce_flag(self._scaler.flag_tensor)
             self._begin(c.world_size, st)
-            check(lib.ps_chunk_step_fused(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
-                                          self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
-                                          c.fp16_multicast_ptr, c.peer_bases.data_ptr(), c.world_size, st),
-                  "ps_chunk_step_fused")
+            if transport == "multimem":
+                check(lib.ps_chunk_step_fused(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
+                                              self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
+                                              c.fp16_multicast_ptr, c.peer_bases.data_ptr(), c.world_size, st),
+                      "ps_chunk_step_fused")
+            elif transport == "p2p":
+                check(lib.ps_chunk_step_p2p(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
+                                            self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
+                                            c.peer_bases.data_ptr(), c.world_size, st), "ps_chunk_step_p2p")
+            else:
+                raise ValueError("transport must be 'multimem' or 'p2p'")
             if getattr(self, "_barrier_buf", None) is None:
                 self._barrier_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
             c.all_reduce_flag(self._barrier_buf)
         return None
 
-    def reduced_gradients(self):
-        """What the fused kernel loads as gradients: per owned chunk the in-switch
-        sum of all ranks' fp16 slots (for tests; call between two barriers)."""
+    def reduced_gradients(self, transport="multimem"):
+        """What the fused kernel loads as gradients: per owned chunk the sum of all
+        ranks' fp16 slots, in-switch ("multimem") or fp32-accumulated over peer
+        loads ("p2p") (for tests; call between two barriers)."""
         c = self.client
         cs = c.layout.chunk_size
         out = []
         with torch.cuda.device(self.device):
             for cid in c.local_ids:
                 dst = torch.empty(cs, dtype=torch.float16, device=self.device)
-                check(lib.ps_multimem_reduce_probe(c.fp16_multicast_ptr + 2 * cid * cs, dst.data_ptr(), cs,
-                                                   self._stream()), "ps_multimem_reduce_probe")
+                if transport == "p2p":
+                    check(lib.ps_p2p_reduce_probe(c.fp16.data_ptr() + 2 * cid * cs, c.fp16.data_ptr(),
+                                                  c.peer_bases.data_ptr(), c.world_size, dst.data_ptr(), cs,
+                                                  self._stream()), "ps_p2p_reduce_probe")
+                else:
+                    check(lib.ps_multimem_reduce_probe(c.fp16_multicast_ptr + 2 * cid * cs, dst.data_ptr(), cs,
+                                                       self._stream()), "ps_multimem_reduce_probe")
                 out.append(dst)
         return out
 

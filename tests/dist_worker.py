@@ -30,7 +30,7 @@ def main():
     cs = 1 << 15
     n_tensors = 3 * world + 1          # -> padded with dummy chunks
     client = ChunkClient(rank=local, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
-                         symmetric=(SCAN == "fused"))
+                         symmetric=(SCAN in ("fused", "p2p")))
     client.append_tensor_list([("w%d" % i, cs - (7 if i == n_tensors - 1 else 0), i % 2)
                                for i in range(n_tensors)])
     client.allocate()
@@ -65,10 +65,10 @@ def main():
         dist.all_gather(allg, grads.to(dev))
         exact = sum(t.double() for t in allg)
         mag = sum(t.double().abs() for t in allg)
-        if SCAN == "fused":
-            # what the fused kernel's in-switch reduction returns for this rank's chunks
+        if SCAN in ("fused", "p2p"):
+            # what the fused kernel's reduction returns for this rank's chunks
             dist.barrier()
-            reduced = opt.reduced_gradients()
+            reduced = opt.reduced_gradients("multimem" if SCAN == "fused" else "p2p")
             torch.cuda.synchronize()
             dist.barrier()
         else:
@@ -90,6 +90,10 @@ def main():
                     # ulp of the exact sum, inside the (world - 1) / 2 ulp a ring of fp16
                     # additions may be off by for world >= 3
                     tol = 2.0 ** -10 * want.abs() + 2.0 ** -24
+                elif SCAN == "p2p":
+                    # fp32 accumulation in rank order (each addition within 2^-24 relative of
+                    # the partial sum), one rounding to fp16
+                    tol = 2.0 ** -11 * want.abs() + world * 2.0 ** -23 * mag[c * cs:(c + 1) * cs] + 2.0 ** -25
                 else:
                     # NCCL adds the `world` fp16 contributions in an order of its own, rounding
                     # to fp16 after every addition: (world - 1) roundings of at most half an ulp
@@ -102,8 +106,8 @@ def main():
                                          "exact %r contributions %r" % (c, i, int(bad.sum()), float(got[i]), float(want[i]),
                                                                         [float(t[c * cs + i]) for t in allg]))
             H.append(got.cpu().numpy().copy())
-        if SCAN == "fused":
-            opt.step_fused_collectives()
+        if SCAN in ("fused", "p2p"):
+            opt.step_fused_collectives("multimem" if SCAN == "fused" else "p2p")
         else:
             opt.step_with_collectives(scan=SCAN)
         skipped = orc.step(H, P, M, V, overflow=poisoned)

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("scan", ["local", "reduced", "fused"])
+@pytest.mark.parametrize("scan", ["local", "reduced", "fused", "p2p"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_chunk_step_with_collectives(world, scan):
     if torch.cuda.device_count() < world:
