@@ -24,9 +24,16 @@ from . import port
 
 
 class StepOracle:
-    def __init__(self, calls, groups, scaler, use_adamw, gradient_clipping=-1, world_size=1):
+    def __init__(self, calls, groups, scaler, use_adamw, gradient_clipping=-1, world_size=1,
+                 trailing_call_group=None):
         """calls: list of (chunk_index, start, end, group) in visiting order.
-        groups: list of dicts lr / betas / eps / weight_decay."""
+        groups: list of dicts lr / betas / eps / weight_decay.
+        trailing_call_group: when the oracle follows only the first tensors of a
+        rank, the group index of the rank's LAST tensor: an empty adam_update
+        call with that group's betas is made after the followed ones, so that
+        the optimizer object's beta^t history (cpu_adam.h:143-162) is the one the
+        full call sequence leaves behind."""
+        self.trailing_call_group = trailing_call_group
         self.calls = list(calls)
         self.groups = groups
         self.scaler = scaler
@@ -87,6 +94,11 @@ class StepOracle:
             out = np.empty(e - s, dtype=np.uint16)
             port.cast_fp32_to_fp16(p, out)
             h16[c].view(np.uint16)[s:e] = out
+        if self.trailing_call_group is not None:
+            hp = self.groups[self.trailing_call_group]
+            e32, e16 = np.zeros(0, dtype=np.float32), np.zeros(0, dtype=np.float16)
+            self.adam.adam_update(self.step_count, hp["lr"], hp["betas"][0], hp["betas"][1], hp["eps"],
+                                  hp["weight_decay"], True, e32, e16, e32.copy(), e32.copy(), loss_scale)
         if self.scaler is not None:
             self.scaler.update_scale(False)
         return False
