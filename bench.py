@@ -55,6 +55,12 @@ def parse_args():
                          "'fused' = one kernel over NVSwitch multicast memory (multimem); 'p2p' = one kernel "
                          "over peer loads / stores; 'auto' = p2p for 2-3 ranks, fused for more, nccl if "
                          "symmetric memory cannot be set up")
+    ap.add_argument("--offload-chunks", type=int, default=0,
+                    help="keep the fp32 state of this many of the rank's chunks in pinned host memory and "
+                         "stream them through the double-buffered offload pipeline (hybrid placement); "
+                         "prints the offload report instead of the headline line")
+    ap.add_argument("--offload-slots", type=int, default=2)
+    ap.add_argument("--offload-piece", type=int, default=16 * 1024 * 1024, help="elements per staged piece")
     return ap.parse_args()
 
 
@@ -534,8 +540,93 @@ def run_e2e(args, client, opt, pristine, world, rank, dev, one_step_fn):
             "what": "pinned host fp16 grads -> slots, step, fp16 params of local chunks + control block -> pinned host"}
 
 
+def run_offload(args):
+    """Hybrid placement: `--offload-chunks` of the rank's chunks keep master / momentum /
+    variance in pinned host memory.  Reports the step time, the three component times of
+    the offloaded part measured alone (host->device copies, kernel, device->host copies)
+    and overlap efficiency = max(component) / (step time - resident-only time)."""
+    import torch
+    from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
+    from patrickstar_b200.offload import OffloadPipeline
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cs, npr, k_off = args.chunk_size, args.chunks, args.offload_chunks
+    client = ChunkClient(rank=0, default_chunk_size=cs, world_size=1, device=dev, pack="flat")
+    client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr)])
+    client.allocate(state_budget_bytes=(npr - k_off) * 12 * cs)
+    assert len(client.local_ids) - client.n_resident == k_off
+    scaler = DynamicLossScaler(device=dev, **SCALER)
+    opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
+    if args.offload_slots != 2 or args.offload_piece != 16 * 1024 * 1024:
+        opt._desc_host = opt._desc_host[:npr].copy()
+        opt._offload = OffloadPipeline(client, opt, n_slots=args.offload_slots, piece_elems=args.offload_piece)
+    gen = torch.Generator(device=dev).manual_seed(1000)
+    tmp = torch.empty(cs, device=dev)
+    for k in range(npr):
+        for t, (mu, sd) in zip(client.chunk_state(k), ((0, 0.02), (0, 1e-4), (0, 1e-6))):
+            tmp.normal_(mu, sd, generator=gen)
+            t.copy_(tmp.abs() if sd == 1e-6 else tmp)
+    pristine = tmp.normal_(0, 8e-3, generator=gen).half()
+
+    def refresh():
+        for c in range(npr):
+            client.fp16_chunk(c).copy_(pristine)
+
+    def timed(fn, n):
+        ev = []
+        for _ in range(n):
+            refresh()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            ev.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in ev) / n
+
+    for _ in range(args.warmup):
+        refresh()
+        opt.step()
+    torch.cuda.synchronize()
+    step_ms = timed(opt.step, args.steps)
+    # components of the offloaded part, each alone on one stream
+    staging = [torch.empty(cs, dtype=torch.float32, device=dev) for _ in range(3)]
+    off = range(client.n_resident, npr)
+
+    def h2d():
+        for k in off:
+            for dst, src in zip(staging, client.chunk_state(k)):
+                dst.copy_(src, non_blocking=True)
+
+    def d2h():
+        for k in off:
+            for src, dst in zip(staging, client.chunk_state(k)):
+                dst.copy_(src, non_blocking=True)
+
+    h2d_ms, d2h_ms = timed(h2d, 3), timed(d2h, 3)
+    # resident-only step time (same launch sequence without the pipeline)
+    pipe, opt._offload = opt._offload, None
+    resident_ms = timed(opt.step, 3)
+    opt._offload = pipe
+    kern_ms = k_off * (BYTES_PER_PARAM * cs / 6.2e12) * 1e3  # from the measured 6.2 TB/s of the step kernel
+    bound = max(h2d_ms, d2h_ms, kern_ms)
+    line = {"workload": "hybrid offload: %d chunks x %d elements, %d resident in HBM, %d in pinned host memory, "
+                        "%d staging slots of %d elements" % (npr, cs, npr - k_off, k_off, args.offload_slots,
+                                                              opt._offload.piece_elems),
+            "metric": METRIC, "unit": UNIT, "value": npr * cs / (step_ms * 1e-3), "ms_per_step": step_ms,
+            "offloaded_params_per_s": k_off * cs / ((step_ms - resident_ms) * 1e-3),
+            "h2d_ms_alone": h2d_ms, "d2h_ms_alone": d2h_ms, "kernel_ms_offloaded_est": kern_ms,
+            "resident_only_ms": resident_ms,
+            "h2d_gbs": 12 * k_off * cs / (h2d_ms * 1e-3) / 1e9, "d2h_gbs": 12 * k_off * cs / (d2h_ms * 1e-3) / 1e9,
+            "overlap_efficiency": bound / (step_ms - resident_ms),
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
+    if args.offload_chunks > 0:
+        return run_offload(args)
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -57,7 +57,10 @@ typedef struct ps_chunk_desc {
     uint32_t numel;    /* elements in use (<= chunk capacity)                   */
     uint32_t seg_begin; /* [seg_begin, seg_end) in the segment table            */
     uint32_t seg_end;
-    uint32_t reserved;
+    uint32_t reserved; /* ps_chunk_step only: first element to process (a multiple of 2048;
+                          0 = whole chunk).  Lets a launch cover the piece [first, numel) of a
+                          chunk whose p32 / exp_avg / exp_avg_sq pointers are biased so that
+                          index `first` is the first staged element (offload pipeline).       */
 } ps_chunk_desc;
 
 /* A run of elements of one chunk that shares hyper-parameters: [start, end)
@@ -285,13 +288,17 @@ int ps_scale_loss(const float* loss_dev, float* out_dev, size_t n, const ps_scal
 /* ------------------------------------------------------------------ */
 #define PS_OFFLOAD_MAX_SLOTS 8
 
-/* One offloaded local chunk: its fp32 master / momentum / variance in PINNED
- * host memory (what the reference keeps as CPU chunks under hybrid placement,
+/* One piece of an offloaded local chunk: `numel` consecutive elements of its
+ * fp32 master / momentum / variance in PINNED host memory (what the reference
+ * keeps as CPU chunks under hybrid placement,
  * patrickstar/ops/fp16_cpu_adam.py:523-528, patrickstar/core/chunk_data.py:275-366)
- * and the index of its descriptor in the device chunk table.  That descriptor's
- * p32 / exp_avg / exp_avg_sq must point at the staging slot (i % n_slots) the
- * i-th chunk of a ps_offload_step call uses; its h16 / numel / segment range are
- * the chunk's own. */
+ * and the index of the piece's descriptor in the device chunk table.  That
+ * descriptor covers [first, first + numel) of the chunk (ps_chunk_desc.reserved
+ * = first, .numel = first + numel) and its p32 / exp_avg / exp_avg_sq point
+ * `first` elements BEFORE the staging slot (i % n_slots) that the i-th piece of
+ * a ps_offload_step call uses, so that chunk-local indices address the slot;
+ * h16 and the segment range are the chunk's own.  Pieces smaller than a chunk
+ * shorten the fill and drain of the pipeline. */
 typedef struct ps_offload_chunk {
     float* p32_host;
     float* exp_avg_host;

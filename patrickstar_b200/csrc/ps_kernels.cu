@@ -476,7 +476,7 @@ chunk_step_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
         const uint32_t c = (uint32_t)(t / tiles_per_chunk);
         const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
         const ps_chunk_desc d = load_desc(chunks + c);
-        const uint32_t tile_base = lt * kTile;
+        const uint32_t tile_base = d.reserved + lt * kTile;  // d.reserved = first element (0 for a whole chunk)
         if (tile_base >= d.numel) continue;
         if (skip)
             step_tile<U, true, true>(d, segs, slots, tile_base);

@@ -18,7 +18,10 @@ from ._lib import CHUNK_DESC_DTYPE, OFFLOAD_CHUNK_DTYPE, check, lib
 
 
 class OffloadPipeline:
-    def __init__(self, client, optimizer, n_slots=2):
+    def __init__(self, client, optimizer, n_slots=2, piece_elems=16 * 1024 * 1024):
+        """n_slots staging slots (2 = double buffering), each 3 fp32 buffers of
+        `piece_elems` elements: a chunk is streamed in pieces of that size, which
+        keeps the pipeline's fill and drain (one copy in, one copy out) short."""
         self.client = client
         self.opt = optimizer
         self.n_slots = n_slots
@@ -26,25 +29,39 @@ class OffloadPipeline:
         dev = client.device
         n_off = len(client.local_ids) - client.n_resident
         self.n_off = n_off
-        # staging slots: 3 fp32 chunk buffers each
-        self.staging = [[torch.empty(cs, dtype=torch.float32, device=dev) for _ in range(3)]
+        piece = min(cs, max(2048, (piece_elems // 2048) * 2048))
+        self.piece_elems = piece
+        self.staging = [[torch.empty(piece, dtype=torch.float32, device=dev) for _ in range(3)]
                         for _ in range(n_slots)]
         self._staging_ptrs = (C.c_void_p * (3 * n_slots))(
             *[t.data_ptr() for slot in self.staging for t in slot])
-        # descriptors of the offloaded chunks: state pointers -> staging slot (i % n_slots)
-        desc = optimizer._desc_host.copy()
-        jobs = np.zeros(n_off, dtype=OFFLOAD_CHUNK_DTYPE)
-        for i in range(n_off):
-            k = client.n_resident + i
-            s = i % n_slots
-            desc["p32"][k], desc["exp_avg"][k], desc["exp_avg_sq"][k] = (
-                t.data_ptr() for t in self.staging[s])
+        base = optimizer._desc_host
+        n_local = len(base)
+        rows, jobs = [], []
+        i = 0
+        for k in range(client.n_resident, n_local):
+            numel = int(base["numel"][k])
             p, m, v = client.chunk_state(k)
-            jobs[i] = (p.data_ptr(), m.data_ptr(), v.data_ptr(), int(desc["numel"][k]), k)
-        self._jobs = jobs
-        check(lib.ps_table_check(desc.ctypes.data, len(desc), optimizer._segs_host.ctypes.data,
-                                 len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
-              "ps_table_check")
+            for first in range(0, numel, piece):
+                count = min(piece, numel - first)
+                s = i % n_slots
+                d = base[k].copy()
+                d["p32"], d["exp_avg"], d["exp_avg_sq"] = (t.data_ptr() - 4 * first for t in self.staging[s])
+                d["numel"] = first + count
+                d["reserved"] = first
+                rows.append(d)
+                jobs.append((p.data_ptr() + 4 * first, m.data_ptr() + 4 * first, v.data_ptr() + 4 * first,
+                             count, n_local + i))
+                i += 1
+        self._jobs = np.array(jobs, dtype=OFFLOAD_CHUNK_DTYPE) if jobs else np.zeros(0, dtype=OFFLOAD_CHUNK_DTYPE)
+        self.n_pieces = len(jobs)
+        # the resident chunks' descriptors are validated as a table; the piece descriptors
+        # share their chunk's (validated) segment range and only narrow [first, numel)
+        if client.n_resident:
+            check(lib.ps_table_check(base.ctypes.data, client.n_resident, optimizer._segs_host.ctypes.data,
+                                     len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
+                  "ps_table_check")
+        desc = np.concatenate([base, np.array(rows, dtype=CHUNK_DESC_DTYPE)]) if rows else base
         optimizer._desc_host = desc
         optimizer._desc_dev = torch.from_numpy(desc.view(np.uint8).copy()).to(dev)
         self._handle = C.c_void_p()
@@ -63,6 +80,6 @@ class OffloadPipeline:
             return
         opt = self.opt
         with torch.cuda.device(self.client.device):
-            check(lib.ps_offload_step(self._handle, self._jobs.ctypes.data, self.n_off, self._staging_ptrs,
+            check(lib.ps_offload_step(self._handle, self._jobs.ctypes.data, self.n_pieces, self._staging_ptrs,
                                       opt._desc_dev.data_ptr(), opt._segs_dev.data_ptr(),
                                       opt._ctrl.data_ptr(), opt._stream()), "ps_offload_step")
