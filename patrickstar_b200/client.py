@@ -69,6 +69,9 @@ class ChunkClient:
     def append_tensor_list(self, specs, shapes=None):
         return self.layout.append_tensor_list(specs, shapes)
 
+    def append_tensor(self, name, numel, group=0, shape=None):
+        return self.layout.append_tensor(name, numel, group, shape)
+
     def register_module(self, module, group_of=None):
         """Register every parameter of an nn.Module, one atomic list per
         sub-module as the reference's pre-process context does
