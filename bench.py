@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--unroll", type=int, default=0, help="kernel tuning knob (0 = library default)")
     ap.add_argument("--blocks-per-sm", type=int, default=-1)
+    ap.add_argument("--bulk", type=int, default=-1, help="kernel tuning knob: 1 = bulk-async staged chunk step")
     ap.add_argument("--scan", default="local", choices=["local", "reduced"],
                     help="N > 1: overflow test on local gradients before the reduction (the reference's "
                          "rule) or on the reduced ones")
@@ -289,6 +290,8 @@ def run_ours(args):
         _lib.tune("unroll", args.unroll)
     if args.blocks_per_sm >= 0:
         _lib.tune("blocks_per_sm", args.blocks_per_sm)
+    if args.bulk >= 0:
+        _lib.tune("bulk", args.bulk)
 
     cs, npr = args.chunk_size, args.chunks
     if args.collectives == "auto":

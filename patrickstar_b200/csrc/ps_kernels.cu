@@ -39,6 +39,7 @@ struct Tuning {
     int unroll = 2;        // 128-bit groups per thread per tile (1, 2 or 4)
     int blocks_per_sm = 0; // 0 = as many as the occupancy calculator allows
     int scan_unroll = 4;
+    int bulk = 0;          // 2..4: chunk step with bulk-async (TMA 1-D) staging, that many stages deep
 };
 Tuning g_tune;
 
@@ -482,6 +483,205 @@ chunk_step_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
             step_tile<U, true, true>(d, segs, slots, tile_base);
         else
             step_tile<U, false, true>(d, segs, slots, tile_base);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Chunk step with bulk-async staging: the four input streams of a tile (fp16
+// grads, fp32 master / momentum / variance; 28 KB per 2048 elements) are brought
+// into shared memory by the copy engine of the SM (cp.async.bulk, completion
+// counted on an mbarrier), kBulkStages tiles deep, so the bytes in flight are
+// bounded by shared memory and not by registers.  One elected thread issues the
+// copies; all threads wait on the stage's barrier, pull their elements out of
+// shared memory, hand the stage back, and compute and store from registers.
+// Every wait is bounded: on a timeout the CTA records an error bit in the
+// control block and leaves.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kBulkTile = kThreads * kVec;  // 2048 elements
+struct __align__(128) BulkStage {
+    uint16_t g[kBulkTile];
+    float p[kBulkTile];
+    float m[kBulkTile];
+    float v[kBulkTile];
+};
+constexpr uint32_t kBulkStageBytes = sizeof(BulkStage);
+static_assert(kBulkStageBytes == 28672, "stage layout");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Streaming data: read once, so the copy carries an evict-first L2 policy like
+// the ld.global.cs of the register path.
+__device__ __forceinline__ uint64_t l2_evict_first_policy()
+{
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar,
+                                          uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+// Bounded wait for the phase with the given parity.  False = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Four consecutive elements of one thread, data already in registers.
+__device__ __forceinline__ void adam_group4(const ps_chunk_desc& d, const ps_segment* segs,
+                                            const ps_hyper_slot* slots, uint32_t e, uint2 gq, float4 pq,
+                                            float4 mq, float4 vq)
+{
+    uint32_t si = d.seg_begin;
+    if (d.seg_end - d.seg_begin > 1) si = find_segment(segs, d.seg_begin, d.seg_end, e);
+    const SegView sv = load_segment(segs, si);
+    if (!(sv.start <= e && e + 4 <= sv.end)) {
+        slow_group<false, true>(d, d.h16, segs, d.seg_begin, d.seg_end, slots, e, e + 4, si, d.h16);
+        return;
+    }
+    const Slot s = load_slot(slots + sv.slot);
+    float p[4] = {pq.x, pq.y, pq.z, pq.w};
+    float m[4] = {mq.x, mq.y, mq.z, mq.w};
+    float v[4] = {vq.x, vq.y, vq.z, vq.w};
+    const uint32_t gw[2] = {gq.x, gq.y};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t h = (k & 1) ? (gw[k >> 1] >> 16) : (gw[k >> 1] & 0xffffu);
+        adam_element(grad_from_half(h, s), p[k], m[k], v[k], s);
+    }
+    __stcs(reinterpret_cast<float4*>(d.p32 + e), make_float4(p[0], p[1], p[2], p[3]));
+    __stcs(reinterpret_cast<float4*>(d.exp_avg + e), make_float4(m[0], m[1], m[2], m[3]));
+    __stcs(reinterpret_cast<float4*>(d.exp_avg_sq + e), make_float4(v[0], v[1], v[2], v[3]));
+    uint2 out;
+    out.x = float_to_half_bits(p[0]) | (float_to_half_bits(p[1]) << 16);
+    out.y = float_to_half_bits(p[2]) | (float_to_half_bits(p[3]) << 16);
+    __stcs(reinterpret_cast<uint2*>(d.h16 + e), out);
+}
+
+template <int kBulkStages>
+__global__ void __launch_bounds__(kThreads)
+chunk_step_bulk_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                       uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
+                       const ps_step_ctrl* __restrict__ ctrl)
+{
+    extern __shared__ __align__(128) unsigned char bulk_smem[];
+    BulkStage* stages = reinterpret_cast<BulkStage*>(bulk_smem);
+    __shared__ uint64_t full_bar[kBulkStages];
+    const ps_hyper_slot* slots = ctrl->slots;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    const uint64_t stride = gridDim.x;
+    if (__ldg(&ctrl->skip)) {
+        // restore path: plain loads, no staging needed (6 B per element)
+        for (uint64_t t = blockIdx.x; t < total; t += stride) {
+            const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+            const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+            const ps_chunk_desc d = load_desc(chunks + c);
+            const uint32_t tile_base = d.reserved + lt * kBulkTile;
+            if (tile_base < d.numel) step_tile<1, true, true>(d, segs, slots, tile_base);
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkStages; ++s) mbar_init(&full_bar[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // producer cursor (thread 0 only): next position of this CTA's tile sequence to look at,
+    // and the number of staged tiles issued so far
+    uint64_t prod_t = blockIdx.x;
+    uint32_t prod_n = 0;
+    const uint64_t policy = l2_evict_first_policy();
+    auto issue_next = [&]() {
+        while (prod_t < total) {
+            const uint32_t c = (uint32_t)(prod_t / tiles_per_chunk);
+            const uint32_t lt = (uint32_t)(prod_t - (uint64_t)c * tiles_per_chunk);
+            const ps_chunk_desc d = load_desc(chunks + c);
+            const uint32_t tile_base = d.reserved + lt * kBulkTile;
+            prod_t += stride;
+            if (tile_base + kBulkTile <= d.numel) {  // a full tile: staged
+                BulkStage* st = &stages[prod_n % kBulkStages];
+                uint64_t* bar = &full_bar[prod_n % kBulkStages];
+                mbar_expect_tx(bar, kBulkStageBytes);
+                bulk_load(st->g, d.h16 + tile_base, sizeof(st->g), bar, policy);
+                bulk_load(st->p, d.p32 + tile_base, sizeof(st->p), bar, policy);
+                bulk_load(st->m, d.exp_avg + tile_base, sizeof(st->m), bar, policy);
+                bulk_load(st->v, d.exp_avg_sq + tile_base, sizeof(st->v), bar, policy);
+                ++prod_n;
+                return;
+            }
+        }
+    };
+    if (threadIdx.x == 0)
+        for (int s = 0; s < kBulkStages; ++s) issue_next();
+
+    uint32_t cons_n = 0;
+    for (uint64_t t = blockIdx.x; t < total; t += stride) {
+        const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+        const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+        const ps_chunk_desc d = load_desc(chunks + c);
+        const uint32_t tile_base = d.reserved + lt * kBulkTile;
+        if (tile_base >= d.numel) continue;
+        if (tile_base + kBulkTile > d.numel) {  // ragged last tile of a chunk: plain path
+            step_tile<1, false, true>(d, segs, slots, tile_base);
+            continue;
+        }
+        const uint32_t s = cons_n % kBulkStages;
+        const bool arrived = mbar_wait(&full_bar[s], (cons_n / kBulkStages) & 1u);
+        if (!__syncthreads_and(arrived)) {
+            if (threadIdx.x == 0) atomicOr(const_cast<int32_t*>(&ctrl->error), 2);
+            return;
+        }
+        // thread i owns elements [4i, 4i+4) and [1024+4i, 1024+4i+4) of the tile:
+        // 16-byte (fp32) and 8-byte (fp16) shared-memory reads with unit stride across the warp
+        const BulkStage* st = &stages[s];
+        const uint32_t o0 = threadIdx.x * 4, o1 = kBulkTile / 2 + threadIdx.x * 4;
+        const uint2 g0 = *reinterpret_cast<const uint2*>(st->g + o0);
+        const uint2 g1 = *reinterpret_cast<const uint2*>(st->g + o1);
+        const float4 p0 = *reinterpret_cast<const float4*>(st->p + o0);
+        const float4 p1 = *reinterpret_cast<const float4*>(st->p + o1);
+        const float4 m0 = *reinterpret_cast<const float4*>(st->m + o0);
+        const float4 m1 = *reinterpret_cast<const float4*>(st->m + o1);
+        const float4 v0 = *reinterpret_cast<const float4*>(st->v + o0);
+        const float4 v1 = *reinterpret_cast<const float4*>(st->v + o1);
+        __syncthreads();  // the stage has been read by everyone: it may be refilled
+        if (threadIdx.x == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_next();
+        }
+        ++cons_n;
+        adam_group4(d, segs, slots, tile_base + o0, g0, p0, m0, v0);
+        adam_group4(d, segs, slots, tile_base + o1, g1, p1, m1, v1);
     }
 }
 
@@ -1028,6 +1228,29 @@ int launch_chunk_step(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t m
     return after_launch();
 }
 
+template <int kBulkStages>
+int launch_chunk_step_bulk(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
+                           const ps_segment* segs, const ps_step_ctrl* ctrl, cudaStream_t st)
+{
+    constexpr int kSmem = kBulkStages * (int)kBulkStageBytes;
+    auto kernel = chunk_step_bulk_kernel<kBulkStages>;
+    PS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kBulkTile - 1) / kBulkTile);
+    uint64_t total = (uint64_t)tpc * n_chunks;
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    int per_sm = g_tune.blocks_per_sm;
+    if (per_sm <= 0) {
+        PS_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, kSmem));
+        if (per_sm < 1) per_sm = 1;
+    }
+    uint64_t g = (uint64_t)di.sm_count * (uint64_t)per_sm;
+    if (g > total) g = total;
+    kernel<<<(int)g, kThreads, kSmem, st>>>(chunks, n_chunks, tpc, segs, ctrl);
+    return after_launch();
+}
+
 int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
                             const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
 {
@@ -1164,6 +1387,9 @@ int ps_tune(const char* key, int value)
     } else if (!strcmp(key, "blocks_per_sm")) {
         if (value < 0 || value > 32) return PS_ERR_INVALID;
         g_tune.blocks_per_sm = value;
+    } else if (!strcmp(key, "bulk")) {
+        if (value != 0 && (value < 2 || value > 4)) return PS_ERR_INVALID;
+        g_tune.bulk = value;
     } else if (!strcmp(key, "scan_unroll")) {
         if (value != 1 && value != 2 && value != 4) return PS_ERR_INVALID;
         g_tune.scan_unroll = value;
@@ -1404,6 +1630,12 @@ int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t m
     if (chunks_dev == nullptr || segs_dev == nullptr || ctrl_dev == nullptr) return PS_ERR_INVALID;
     if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
     cudaStream_t st = (cudaStream_t)stream;
+    switch (g_tune.bulk) {  // bulk-async staged variant, N stages deep
+        case 2: return launch_chunk_step_bulk<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        case 3: return launch_chunk_step_bulk<3>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        case 4: return launch_chunk_step_bulk<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
+        default: break;
+    }
     switch (g_tune.unroll) {
         case 1: return launch_chunk_step<1>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);
         case 4: return launch_chunk_step<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, st);

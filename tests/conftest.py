@@ -12,6 +12,18 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
 
 
+@pytest.fixture(scope="session", autouse=True)
+def _kernel_variant_from_env():
+    """PS_TEST_TUNE="bulk=1,unroll=1" runs the GPU tests on another kernel variant."""
+    spec = os.environ.get("PS_TEST_TUNE", "")
+    if spec:
+        from patrickstar_b200 import _lib
+        for kv in spec.split(","):
+            k, v = kv.split("=")
+            _lib.tune(k.strip(), int(v))
+    yield
+
+
 @pytest.fixture(scope="session")
 def oracle_port():
     from oracle import port
