@@ -23,8 +23,8 @@ chunk belongs to rank ``k % world`` and to communication group ``k // world``;
 the list is padded with dummy chunks to a multiple of ``world``
 (patrickstar/core/preprocess.py:335-339).
 """
-from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
 
 import numpy as np
 

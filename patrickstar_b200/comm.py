@@ -8,7 +8,6 @@ patrickstar/core/client.py:481-485, 831-836, which makes torch gather the list
 into a temporary first).  Works on CUDA tensors over NCCL (the product path)
 and on CPU tensors over gloo (host-logic tests).
 """
-import torch
 import torch.distributed as dist
 
 

@@ -29,7 +29,7 @@ import torch
 
 from ._lib import (CHUNK_DESC_DTYPE, PS_MAX_GROUPS, SEGMENT_DTYPE, GroupHyper, ScalerState, StepCtrl,
                    StepPlan, check, lib)
-from .loss_scaler import DynamicLossScaler, LossScaler, _DeviceScaler
+from .loss_scaler import DynamicLossScaler, _DeviceScaler
 
 
 class _NoScaler(_DeviceScaler):

@@ -12,7 +12,6 @@ import ctypes as C
 
 import torch
 
-from . import _lib
 from ._lib import ScalerState, check, lib
 
 
@@ -173,8 +172,12 @@ class DynamicLossScaler(_DeviceScaler):
             return False
         if not x.is_cuda:
             raise TypeError("patrickstar_b200 checks gradients on the GPU only")
-        g = x if x.dtype == torch.float16 else x.to(torch.float16)
-        g = g.contiguous()
+        if x.dtype != torch.float16:
+            # not a chunk gradient (the reference's fp32 grads of torch-managed
+            # params): the reference's own formulation, literally
+            cpu_sum = float(x.float().sum())
+            return cpu_sum == float("inf") or cpu_sum == -float("inf") or cpu_sum != cpu_sum
+        g = x.contiguous()
         flag = torch.zeros(1, dtype=torch.int32, device=x.device)
         with torch.cuda.device(x.device):
             check(lib.ps_overflow_scan_buffer(g.data_ptr(), g.numel(), flag.data_ptr(),

@@ -3,7 +3,6 @@ tests/test_gpu_multi.py with torch.distributed.run, one rank per GPU (NCCL)."""
 import os
 import sys
 
-import numpy as np
 import torch
 import torch.distributed as dist
 

@@ -110,9 +110,6 @@ def test_compute_entry_points_refuse_without_arguments(L):
 
 def test_package_import_is_lazy_and_fails_loudly_without_library(tmp_path, monkeypatch):
     """No fallback: with the shared library missing, importing a compute name raises."""
-    import importlib
-    import sys
-    import patrickstar_b200
     from patrickstar_b200 import _lib
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "missing.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):

@@ -251,7 +251,6 @@ def test_full_chunk_config0_against_reference_checksums(golden_dir):
 
 
 def test_table_validation_rejects_bad_tables():
-    import ctypes as C
     from patrickstar_b200._lib import (CHUNK_DESC_DTYPE, PS_ERR_ALIGN, PS_ERR_INVALID, PS_ERR_TABLE,
                                        SEGMENT_DTYPE, lib)
     d = np.zeros(1, dtype=CHUNK_DESC_DTYPE)

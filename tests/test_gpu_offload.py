@@ -2,7 +2,6 @@
 through staging slots; results must equal the all-resident run and the oracle
 bit for bit, over several steps (slot reuse across steps) and through a skipped
 step."""
-import numpy as np
 import pytest
 import torch
 
