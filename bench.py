@@ -33,6 +33,10 @@ SCALER = dict(init_scale=2 ** 3, scale_factor=2, scale_window=1000, min_scale=1)
 METRIC = "adam_updated_params_per_sec"
 UNIT = "params/s"
 BYTES_PER_PARAM = 28  # fp16 grad 2 + fp32 p/m/v read 12 + write 12 + fp16 param 2
+# DRAM traffic of chunk_step_kernel per parameter from the ncu capture of the 2-chunk case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 3.702 GB for 134,217,728 parameters);
+# traffic grows linearly with the number of chunks, so a launch is scaled by its parameters
+NCU_DRAM_BYTES_PER_PARAM = 3.702e9 / (2 * 64 * 1024 * 1024)
 
 
 def parse_args():
@@ -164,9 +168,9 @@ def cpu_adam_call(kind, impl, handle, step, p, g, m, v):
                            HYPER["weight_decay"], True, p, g, m, v, 8.0)
 
 
-def cpu_baseline(n, calls=20, warm=3):
+def cpu_baseline(n, seconds=10.0, max_calls=2000, warm=3):
     """Times adam_update of the CPU implementation on one chunk with all host
-    threads.  Bounded sample: 1 chunk, `calls` calls."""
+    threads.  Bounded sample: 1 chunk, about `seconds` of calls."""
     import torch
     kind, impl = _load_cpu_impl()
     cores = torch.get_num_threads()
@@ -181,10 +185,12 @@ def cpu_baseline(n, calls=20, warm=3):
     for i in range(warm):
         cpu_adam_call(kind, impl, handle, 1 + i, p, g, m, v)
     ts = []
-    for i in range(calls):
+    t_begin = time.perf_counter()
+    while len(ts) < max_calls and (time.perf_counter() - t_begin < seconds or len(ts) < 10):
         t0 = time.perf_counter()
-        cpu_adam_call(kind, impl, handle, 1 + warm + i, p, g, m, v)
+        cpu_adam_call(kind, impl, handle, 1 + warm + len(ts), p, g, m, v)
         ts.append(time.perf_counter() - t0)
+    calls = len(ts)
     if kind == "reference":
         impl.destroy_adam(31337)
     ts.sort()
@@ -408,7 +414,6 @@ def run_ours(args):
         total_ms = float(t.item())
     ctrl = opt.read_ctrl()
     assert ctrl.step == args.warmup + args.steps and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
-    launches_note = launches
     params_per_step = npr * cs * world
     value = params_per_step * args.steps / (total_ms * 1e-3)
 
@@ -432,7 +437,9 @@ def run_ours(args):
         achieved = bytes_per_launch / (kern_avg_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "chunk_step_kernel", "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
-                    "traffic": None, "algorithmic_bytes_per_launch": bytes_per_launch,
+                    "traffic": NCU_DRAM_BYTES_PER_PARAM * bytes_per_launch / BYTES_PER_PARAM,
+                    "traffic_source": "ncu capture of the 2-chunk case, scaled by parameters per launch",
+                    "algorithmic_bytes_per_launch": bytes_per_launch,
                     "launch_ms": kern_avg_ms, "launches_timed": len(kernel_ev)}
 
     local_step = None

@@ -103,6 +103,14 @@ class ChunkClient:
         per_chunk = 3 * 4 * cs
         if state_budget_bytes is None:
             self.n_resident = n_local
+        elif state_budget_bytes == "auto":
+            # what the reference derives from its memory tracer: the chunks that fit
+            # into the GPU memory left over, scaled by margin_use_ratio
+            # (patrickstar/core/memtracer/memtracer.py:190-227, default ratio 0.8)
+            ratio = (self.config.get("mem_tracer", {}) or {}).get("margin_use_ratio", 0.8)
+            free, _ = torch.cuda.mem_get_info(self.device)
+            free -= 2 * lay.n_chunks * cs  # the fp16 chunk list allocated below
+            self.n_resident = max(0, min(n_local, int(free * ratio) // per_chunk))
         else:
             self.n_resident = max(0, min(n_local, int(state_budget_bytes) // per_chunk))
         n_off = n_local - self.n_resident

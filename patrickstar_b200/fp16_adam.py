@@ -30,6 +30,7 @@ import torch
 from ._lib import (CHUNK_DESC_DTYPE, PS_MAX_GROUPS, SEGMENT_DTYPE, GroupHyper, ScalerState, StepCtrl,
                    StepPlan, check, lib)
 from .loss_scaler import DynamicLossScaler, _DeviceScaler
+from .timers import ADAM, ADAM_COMPUTE, ADAM_OFFLOAD, ADAM_OVERFLOW_SCAN, PhaseTimer
 
 
 class _NoScaler(_DeviceScaler):
@@ -95,6 +96,9 @@ class FP16Adam(torch.optim.Optimizer):
         lay._piece_cache = None
         lay._by_chunk = None
 
+        # section timing of the step on CUDA events (off by default; no sync either way)
+        self.time_profile = False
+        self.timer = PhaseTimer()
         self._calls = 0            # number of step() calls, an upper bound of the step counter
         self._pow_len = 0
         self._pow_table = None
@@ -197,17 +201,34 @@ class FP16Adam(torch.optim.Optimizer):
         c = self.client
         if grad_divisor is None:
             grad_divisor = c.world_size if c.world_size > 1 else 0
+        tp = self.time_profile
         with torch.cuda.device(self.device):
             st = self._stream()
+            if tp:
+                self.timer.start_profile(ADAM)
             if self._dynamic:
                 if scan and self._n_local:
+                    if tp:
+                        self.timer.start_profile(ADAM_OVERFLOW_SCAN)
                     check(lib.ps_overflow_scan(self._desc_dev.data_ptr(), self._n_local, self._max_numel,
                                                self._scaler.flag_ptr, st), "ps_overflow_scan")
+                    if tp:
+                        self.timer.finish_profile(ADAM_OVERFLOW_SCAN)
                 c.all_reduce_flag(self._scaler.flag_tensor)
             self._begin(grad_divisor, st)
+            if tp:
+                self.timer.start_profile(ADAM_COMPUTE)
             self._update_resident(st)
+            if tp:
+                self.timer.finish_profile(ADAM_COMPUTE)
             if self._offload is not None:
+                if tp:
+                    self.timer.start_profile(ADAM_OFFLOAD)
                 self._offload.run()
+                if tp:
+                    self.timer.finish_profile(ADAM_OFFLOAD)
+            if tp:
+                self.timer.finish_profile(ADAM)
         return loss
 
     def _begin(self, grad_divisor, st):

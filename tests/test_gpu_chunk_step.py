@@ -273,3 +273,23 @@ def test_table_validation_rejects_bad_tables():
     assert chk() == PS_ERR_ALIGN
     d["h16"] = 0
     assert chk() == PS_ERR_INVALID
+
+
+def test_section_timers_and_auto_placement():
+    """CUDA-event section timers under the reference's key names, and the
+    memory-derived hybrid placement (everything fits here, so all chunks stay
+    resident)."""
+    from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
+    cs = 1 << 16
+    c = ChunkClient(rank=0, default_chunk_size=cs, world_size=1, device=DEV, pack="flat")
+    c.append_tensor_list([("w%d" % i, cs, 0) for i in range(3)])
+    c.allocate(state_budget_bytes="auto")
+    assert c.n_resident == 3
+    opt = FP16Adam(c, c.params.values(), loss_scaler=DynamicLossScaler(init_scale=8), lr=1e-3)
+    opt.time_profile = True
+    for _ in range(3):
+        opt.step()
+    summ = opt.timer.summary()
+    assert list(summ) == ["ADAM_overflow_scan", "ADAM_compute", "ADAM"]
+    assert all(calls == 3 and ms > 0 for calls, ms in summ.values())
+    assert summ["ADAM"][1] >= summ["ADAM_compute"][1]
