@@ -508,8 +508,15 @@ def run_e2e(args, client, opt, pristine, world, rank, dev, one_step_fn):
     host_out = torch.empty(npr * cs, dtype=torch.float16).pin_memory()
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
+    outs = [host_out[k * cs:(k + 1) * cs] for k in range(npr)]
+    ins = [host_in[:cs]] * npr
 
     def e2e_step():
+        if world == 1:
+            # the public call for host-resident fp16 chunks: copies, scan, step and
+            # write-back pipelined chunk by chunk
+            opt.step_host_chunks(ins, outs)
+            return opt.read_ctrl()  # device -> host read of the step's result (skip flag, step counter)
         evs = []
         with torch.cuda.stream(copy_in):
             for g in range(npr):

@@ -248,6 +248,55 @@ class FP16Adam(torch.optim.Optimizer):
                                 self._segs_dev.data_ptr(), self._ctrl.data_ptr(), st), "ps_chunk_step")
 
     @torch.no_grad()
+    def step_host_chunks(self, host_grads, host_params_out):
+        """One step for a caller that keeps the fp16 chunks in (pinned) host memory,
+        as the reference does for fp16 chunks it has evicted to the CPU
+        (patrickstar/ops/chunk_io_buff.py:214-255 copies such a grad chunk to the
+        compute device, :85-128 writes the params back).
+
+        host_grads[k] / host_params_out[k]: pinned fp16 host tensors for the k-th
+        local chunk.  Pipeline, no host synchronisation: chunk k's gradients are
+        copied in on a side stream and scanned as they arrive; after the last one
+        the skip decision is taken; then chunk k is updated and its fp16 params
+        are copied out on a second side stream while chunk k+1 is updated.
+        Single rank, resident chunks only."""
+        c = self.client
+        if c.world_size != 1 or self._offload is not None:
+            raise NotImplementedError("step_host_chunks: single rank, all chunks resident")
+        n = self._n_local
+        if len(host_grads) != n or len(host_params_out) != n:
+            raise ValueError("need one host tensor per local chunk")
+        if getattr(self, "_io_streams", None) is None:
+            self._io_streams = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
+        s_in, s_out = self._io_streams
+        main = torch.cuda.current_stream(self.device)
+        item = CHUNK_DESC_DTYPE.itemsize
+        with torch.cuda.device(self.device):
+            st = self._stream()
+            s_in.wait_stream(main)
+            for k, cid in enumerate(c.local_ids):
+                numel = int(self._desc_host["numel"][k])
+                with torch.cuda.stream(s_in):
+                    c.fp16_chunk(cid)[:numel].copy_(host_grads[k][:numel], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                main.wait_event(ev)
+                if self._dynamic and numel:
+                    check(lib.ps_overflow_scan(self._desc_dev.data_ptr() + k * item, 1, numel,
+                                               self._scaler.flag_ptr, st), "ps_overflow_scan")
+            self._begin(0, st)
+            for k, cid in enumerate(c.local_ids):
+                numel = int(self._desc_host["numel"][k])
+                self._update_resident(st, first=k, count=1)
+                ev = torch.cuda.Event()
+                ev.record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev)
+                    host_params_out[k][:numel].copy_(c.fp16_chunk(cid)[:numel], non_blocking=True)
+            main.wait_stream(s_out)
+        return None
+
+    @torch.no_grad()
     def step_with_collectives(self, scan="local"):
         """The multi-GPU chunk step: per communication group a reduce-scatter of the
         fp16 grad chunks, the rank-local fused step, and an all-gather of the fp16

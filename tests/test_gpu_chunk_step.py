@@ -293,3 +293,93 @@ def test_section_timers_and_auto_placement():
     assert list(summ) == ["ADAM_overflow_scan", "ADAM_compute", "ADAM"]
     assert all(calls == 3 and ms > 0 for calls, ms in summ.values())
     assert summ["ADAM"][1] >= summ["ADAM_compute"][1]
+
+
+def test_device_error_word_when_pow_table_is_short():
+    """Failure detection without a fault: the step-begin kernel finds the beta^t
+    table shorter than its step counter, falls back to computing the powers
+    itself and sets the sticky error bit, which the host reads as an error."""
+    import ctypes as C
+    from patrickstar_b200 import _lib as L
+    lib = L.lib
+    stream = C.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+    ctrl_dev = torch.zeros(C.sizeof(L.StepCtrl), dtype=torch.uint8, device=DEV)
+    scaler_dev = torch.zeros(C.sizeof(L.ScalerState), dtype=torch.uint8, device=DEV)
+    flag_dev = torch.zeros(1, dtype=torch.int32, device=DEV)
+    L.check(lib.ps_ctrl_init(ctrl_dev.data_ptr(), 40, 0.9, 0.999, stream), "ps_ctrl_init")
+    init = L.ScalerState(cur_scale=8.0, scale_factor=2.0, min_scale=1.0, cur_iter=0, last_overflow_iter=-1,
+                         scale_window=1000, delayed_shift=1, cur_hysteresis=1, consecutive_hysteresis=0, dynamic=1)
+    L.check(lib.ps_scaler_init(scaler_dev.data_ptr(), C.byref(init), stream), "ps_scaler_init")
+    tab = np.zeros((8, 2), dtype=np.float32)
+    L.check(lib.ps_pow_table_fill(0.9, 0.999, 0, 8, tab.ctypes.data), "ps_pow_table_fill")
+    tab_dev = torch.from_numpy(tab).to(DEV)
+    plan = L.StepPlan()
+    plan.groups[0] = L.GroupHyper(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, adamw_mode=0)
+    plan.n_groups, plan.first_group, plan.last_group, plan.n_calls, plan.bias_correction = 1, 0, 0, 2, 1
+    L.check(lib.ps_step_begin(ctrl_dev.data_ptr(), scaler_dev.data_ptr(), flag_dev.data_ptr(), C.byref(plan),
+                              tab_dev.data_ptr(), 8, stream), "ps_step_begin")   # step 41 >= table length 8
+    out = L.StepCtrl()
+    L.check(lib.ps_ctrl_read(ctrl_dev.data_ptr(), C.byref(out), stream), "ps_ctrl_read")
+    assert out.error & 1 and out.step == 41 and out.skip == 0
+    import math
+    want = np.float32(math.pow(float(np.float32(0.9)), 41))
+    assert abs(out.betta1_t - want) <= 2 * np.spacing(want)   # the fallback is close, the bit says "not pinned"
+    # the optimizer surfaces it
+    from patrickstar_b200 import FP16Adam
+    client = make_client([("w", 256, 0)], 256)
+    opt = FP16Adam(client, client.params.values(), lr=1e-3)
+    opt._calls = 10 ** 6          # pretend the host lost track ...
+    opt._pow_len = 10 ** 7        # ... and believes the table is long enough
+    opt._pow_table = torch.zeros(2, 2, device=DEV)
+    plan2 = opt._plan(0)
+    L.check(lib.ps_ctrl_init(opt._ctrl.data_ptr(), 100, 0.9, 0.999, stream), "ps_ctrl_init")
+    L.check(lib.ps_step_begin(opt._ctrl.data_ptr(), opt._scaler.state_ptr, opt._scaler.flag_ptr, C.byref(plan2),
+                              opt._pow_table.data_ptr(), 2, stream), "ps_step_begin")
+    with pytest.raises(RuntimeError, match="device-side error word"):
+        opt.read_ctrl()
+
+
+def test_step_host_chunks_equals_step():
+    """The pipelined step for host-resident fp16 chunks gives the bits of the
+    plain step, over a skipped step too."""
+    from patrickstar_b200 import DynamicLossScaler, FP16Adam
+    cs = 20000
+    specs = [("a", 15000, 0), ("b", 30000, 1), ("c", 12000, 0)]
+    out = []
+    for streamed in (False, True):
+        client = make_client(specs, cs)
+        g0 = [client.params["a"], client.params["c"]]
+        opt = FP16Adam(client, [{"params": g0, "weight_decay": 0.01}, {"params": [client.params["b"]]}],
+                       loss_scaler=DynamicLossScaler(init_scale=16), lr=1e-3, use_adamw=True)
+        fill_states(client, 77)
+        gen = torch.Generator().manual_seed(78)
+        n_local = len(client.local_ids)
+        hin = [torch.empty(cs, dtype=torch.float16).pin_memory() for _ in range(n_local)]
+        hout = [torch.zeros(cs, dtype=torch.float16).pin_memory() for _ in range(n_local)]
+        for step in range(4):
+            for k, cid in enumerate(client.local_ids):
+                g = (torch.randn(cs, generator=gen) * 1e-2).half()
+                if step == 2 and k == 1:
+                    g[11] = float("nan")
+                hin[k].copy_(g)
+                if not streamed:
+                    client.fp16_chunk(cid).copy_(g)
+            if streamed:
+                opt.step_host_chunks(hin, hout)
+            else:
+                opt.step()
+        torch.cuda.synchronize()
+        state = [[t.clone() for t in client.chunk_state(k)] for k in range(n_local)]
+        fp16 = [client.fp16_chunk(c)[:client.layout.chunk_numel(c)].clone() for c in client.local_ids]
+        if streamed:
+            for k, c in enumerate(client.local_ids):
+                n_used = client.layout.chunk_numel(c)
+                assert torch.equal(hout[k][:n_used].view(torch.int16), fp16[k].cpu().view(torch.int16))
+        out.append((state, fp16, opt.step_count, opt.skipped_steps))
+    (sa, fa, ca, ka), (sb, fb, cb, kb) = out
+    assert (ca, ka) == (cb, kb) == (3, 1)
+    for x, y in zip(sa, sb):
+        for t, u in zip(x, y):
+            assert torch.equal(t.view(torch.int32), u.view(torch.int32))
+    for t, u in zip(fa, fb):
+        assert torch.equal(t.view(torch.int16), u.view(torch.int16))
