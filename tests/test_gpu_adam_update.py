@@ -157,3 +157,37 @@ def test_error_codes(op):
         op.destroy_adam(99999)
     with pytest.raises(TypeError):
         op.adam_update(0, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, True, x.cpu(), x.half(), x, x, -1)
+
+
+def test_special_values_bit_exact(op, oracle_port):
+    """IEEE corner cases: signed zeros, subnormal halves and floats, the largest
+    half, zero and tiny variance, huge and tiny masters — no flush-to-zero, same
+    roundings as the CPU lanes."""
+    dev = torch.device("cuda:0")
+    tiny32 = np.float32(1e-45)
+    specials_p = [0.0, -0.0, 1e-38, -1e-38, float(tiny32), 3e38, -3e38, 1.0, 65504.0, 1e-20]
+    specials_v = [0.0, float(tiny32), 1e-38, 1e-30, 1e-12, 1.0, 1e30, 3e38, 2e-45, 1e-24]
+    specials_g = [0.0, -0.0, 6e-8, -6e-8, 6.1e-5, 65504.0, -65504.0, 1.0, 1e-4, 3e-7]  # 6e-8: smallest subnormal half
+    n = 16 * len(specials_p) * len(specials_v)
+    P = torch.tensor(specials_p, dtype=torch.float32).repeat_interleave(len(specials_v)).repeat(16)
+    V = torch.tensor(specials_v, dtype=torch.float32).repeat(len(specials_p)).repeat(16)
+    M = (torch.arange(n, dtype=torch.float32) - n / 2) * 1e-9
+    M[::7] = 0.0
+    M[3::11] = float(tiny32)
+    G = torch.tensor(specials_g, dtype=torch.float32).repeat(n // len(specials_g)).roll(3).half()
+    assert P.numel() == V.numel() == G.numel() == n
+    for adamw, wd, scale in ((False, 0.0, -1.0), (False, 0.1, 1024.0), (True, 0.1, 3.0), (True, 0.0, 65536.0)):
+        p, m, v = P.clone(), M.clone(), V.clone()
+        o = oracle_port.OracleAdam(1e-3, 0.9, 0.999, 1e-8, wd, adamw)
+        pd, md, vd, gd = P.to(dev), M.to(dev), V.to(dev), G.to(dev)
+        op.create_adam(7400, 1e-3, 0.9, 0.999, 1e-8, wd, adamw, False)
+        for step in (1, 2):
+            o.adam_update(step, 1e-3, 0.9, 0.999, 1e-8, wd, True, p, G.clone(), m, v, scale)
+            op.adam_update(7400, step, 1e-3, 0.9, 0.999, 1e-8, wd, True, pd, gd, md, vd, scale)
+        op.destroy_adam(7400)
+        for name, a, b in (("p", pd, p), ("m", md, m), ("v", vd, v)):
+            a = a.cpu().numpy()
+            b = b.numpy()
+            nan = np.isnan(b)
+            assert (np.isnan(a) == nan).all(), (name, adamw, wd, scale)
+            assert (a[~nan].view(np.uint32) == b[~nan].view(np.uint32)).all(), (name, adamw, wd, scale)
