@@ -207,6 +207,14 @@ int ps_overflow_scan(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_
 /* Same test on one plain fp16 buffer (FP16Adam.check_overflow on one grad). */
 int ps_overflow_scan_buffer(const uint16_t* g_dev, size_t n, int32_t* flag_dev, void* stream);
 
+/* Gradient hand-off of the backward pass — what the reference's post-backward
+ * hook does per parameter with a host sync (patrickstar/core/hook.py:212-216:
+ * check_overflow(param), then the gradient is copied into the parameter's fp16
+ * slot in the chunk): one pass that copies grad_dev[0..n) into slot_dev[0..n)
+ * and ORs 1 into *flag_dev (may be NULL: copy only) when an inf or nan is seen.
+ * No synchronisation.  A step fed this way can skip its own overflow scan. */
+int ps_grad_handoff(const uint16_t* grad_dev, uint16_t* slot_dev, size_t n, int32_t* flag_dev, void* stream);
+
 /* Head of FP16Adam.step (fp16_cpu_adam.py:549-606, 624-625) as one
  * single-thread kernel, no host sync: reads *flag_dev (already MAX-reduced
  * over ranks); on overflow sets ctrl->skip, otherwise increments the step

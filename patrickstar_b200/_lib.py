@@ -102,6 +102,7 @@ SIGNATURES = {
     "ps_scaler_init": (C.c_int, [_p, C.POINTER(ScalerState), _p]),
     "ps_overflow_scan": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p]),
     "ps_overflow_scan_buffer": (C.c_int, [_p, C.c_size_t, _p, _p]),
+    "ps_grad_handoff": (C.c_int, [_p, _p, C.c_size_t, _p, _p]),
     "ps_step_begin": (C.c_int, [_p, _p, _p, C.POINTER(StepPlan), _p, C.c_uint64, _p]),
     "ps_scaler_update": (C.c_int, [_p, _p, C.c_int, _p]),
     "ps_chunk_step": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p]),

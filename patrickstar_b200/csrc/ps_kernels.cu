@@ -942,6 +942,48 @@ overflow_scan_buffer_kernel(const uint16_t* __restrict__ g, size_t n, size_t hea
     if (__syncthreads_or(found != 0) && threadIdx.x == 0) atomicOr(flag, 1);
 }
 
+// Gradient hand-off of the backward pass (patrickstar/core/hook.py:212-216): the
+// parameter's fp16 gradient is tested for inf/nan and copied into the
+// parameter's fp16 slot in ONE pass (2 B read + 2 B written per element), so the
+// step needs no separate scan of these elements.
+__global__ void __launch_bounds__(kThreads)
+grad_handoff_kernel(const uint16_t* __restrict__ g, uint16_t* __restrict__ slot, size_t n, size_t head,
+                    int vec_ok, int32_t* flag)
+{
+    uint32_t found = 0;
+    if (vec_ok) {
+        const size_t n_vec = (n - head) / kVec;
+        const uint4* src = reinterpret_cast<const uint4*>(g + head);
+        uint4* dst = reinterpret_cast<uint4*>(slot + head);
+        for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n_vec;
+             i += (size_t)gridDim.x * kThreads) {
+            uint4 q = ld_stream(src + i);
+            found |= nonfinite2(q.x) | nonfinite2(q.y) | nonfinite2(q.z) | nonfinite2(q.w);
+            dst[i] = q;
+        }
+        if (blockIdx.x == 0) {
+            for (size_t i = threadIdx.x; i < head; i += kThreads) {
+                uint16_t h = g[i];
+                found |= ((h & 0x7c00u) == 0x7c00u);
+                slot[i] = h;
+            }
+            for (size_t i = head + n_vec * kVec + threadIdx.x; i < n; i += kThreads) {
+                uint16_t h = g[i];
+                found |= ((h & 0x7c00u) == 0x7c00u);
+                slot[i] = h;
+            }
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n;
+             i += (size_t)gridDim.x * kThreads) {
+            uint16_t h = g[i];
+            found |= ((h & 0x7c00u) == 0x7c00u);
+            slot[i] = h;
+        }
+    }
+    if (__syncthreads_or(found != 0) && threadIdx.x == 0 && flag != nullptr) atomicOr(flag, 1);
+}
+
 // ---------------------------------------------------------------------------
 // step-begin: skip decision, step counter, beta^t history, hyper slots,
 // loss-scale update.  One thread.
@@ -1598,6 +1640,29 @@ int ps_overflow_scan_buffer(const uint16_t* g_dev, size_t n, int32_t* flag_dev, 
     if (grid < 1) grid = 1;
     overflow_scan_buffer_kernel<1><<<grid, kThreads, 0, (cudaStream_t)stream>>>(g_dev, n, head,
                                                                                flag_dev);
+    return after_launch();
+}
+
+int ps_grad_handoff(const uint16_t* grad_dev, uint16_t* slot_dev, size_t n, int32_t* flag_dev, void* stream)
+{
+    if (n == 0) return PS_OK;
+    if (grad_dev == nullptr || slot_dev == nullptr) return PS_ERR_INVALID;
+    if (((uintptr_t)grad_dev | (uintptr_t)slot_dev) & 1u) return PS_ERR_ALIGN;
+    // vector path when source and slot reach a 16-byte boundary after the same number of elements
+    const size_t hg = ((16u - ((uintptr_t)grad_dev & 15u)) & 15u) >> 1;
+    const size_t hs = ((16u - ((uintptr_t)slot_dev & 15u)) & 15u) >> 1;
+    const int vec_ok = (hg == hs);
+    size_t head = hg < n ? hg : n;
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    uint64_t work = vec_ok ? (n - head) / kVec : n;
+    uint64_t blocks = (work + kThreads - 1) / kThreads;
+    uint64_t cap = (uint64_t)di.sm_count * 8u;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (grid < 1) grid = 1;
+    grad_handoff_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(grad_dev, slot_dev, n, head, vec_ok,
+                                                                    flag_dev);
     return after_launch();
 }
 

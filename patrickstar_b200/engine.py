@@ -106,13 +106,15 @@ class ChunkStepEngine(torch.nn.Module):
             self.loss_scaler.backward(loss)
         else:
             loss.backward()
-        with torch.no_grad():
-            for p in self.module.parameters():
-                if p.grad is None:
-                    continue
-                self.optimizer.check_overflow(p)
-                p.data.copy_(p.grad)
-                p.grad = None
+        for p in self.module.parameters():
+            self.optimizer.handoff_grad(p)   # overflow test + copy into the slot, one pass
+        self._grads_scanned = True
+
+    def step(self):
+        """optimizer.step() without a second overflow scan when every gradient came
+        through ``backward`` above."""
+        scanned, self._grads_scanned = getattr(self, "_grads_scanned", False), False
+        return self.optimizer.step(scan=not scanned)
 
 
 def initialize_engine(model_func, local_rank, config=None, client=None):

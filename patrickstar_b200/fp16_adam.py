@@ -187,6 +187,24 @@ class FP16Adam(torch.optim.Optimizer):
             self._scaler.accumulate_overflow(param.grad)
 
     @torch.no_grad()
+    def handoff_grad(self, param):
+        """The backward hook's per-parameter work (patrickstar/core/hook.py:212-216)
+        as one kernel: test ``param.grad`` for inf/nan into the device flag and copy
+        it into the parameter's fp16 slot, then drop ``param.grad``.  No host sync.
+        A step whose gradients all arrived this way may run with ``scan=False``."""
+        g = param.grad
+        if g is None:
+            return
+        if g.dtype != torch.float16 or not g.is_cuda:
+            raise TypeError("handoff_grad needs a CUDA fp16 gradient, got %s on %s" % (g.dtype, g.device))
+        g = g.contiguous()
+        flag = self._scaler.flag_ptr if self._dynamic else None
+        with torch.cuda.device(self.device):
+            check(lib.ps_grad_handoff(g.data_ptr(), param.data.data_ptr(), g.numel(), flag, self._stream()),
+                  "ps_grad_handoff")
+        param.grad = None
+
+    @torch.no_grad()
     def step(self, closure=None, grad_divisor=None, scan=True):
         """One optimizer step over this rank's local chunks (fp16_cpu_adam.py:472-628).
 

@@ -139,3 +139,52 @@ def test_optimizer_checkpoint_round_trip():
     assert oa.step_count == ob.step_count == 9
     assert sa.read_state().cur_scale == sb.read_state().cur_scale
     assert sa.cur_iter == sb.cur_iter == 10
+
+
+def test_grad_handoff_copies_and_flags():
+    """ps_grad_handoff through the C ABI: bit copy at every alignment, flag set
+    exactly when an inf/nan is present (the per-parameter check + copy of the
+    reference's backward hook, patrickstar/core/hook.py:212-216)."""
+    import ctypes as C
+    from patrickstar_b200._lib import check, lib
+    stream = C.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+    gen = torch.Generator().manual_seed(9)
+    for n in (0, 1, 7, 8, 9, 1000, 4099, 1 << 18):
+        for so, do in ((0, 0), (3, 3), (1, 5), (8, 0), (2, 11)):
+            for bad in (None, float("inf"), float("nan"), -float("inf")):
+                src = (torch.randn(n + 32, generator=gen) * 10).half()
+                pos = None
+                if bad is not None and n:
+                    pos = int(torch.randint(0, n, (1,), generator=gen))
+                    src[so + pos] = bad
+                src_d = src.to(DEV)
+                dst_d = torch.full((n + 32,), 7.0, dtype=torch.float16, device=DEV)
+                flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+                check(lib.ps_grad_handoff(src_d.data_ptr() + 2 * so, dst_d.data_ptr() + 2 * do, n, flag.data_ptr(),
+                                          stream), "ps_grad_handoff")
+                out = dst_d.cpu()
+                assert torch.equal(out[do:do + n].view(torch.int16), src[so:so + n].view(torch.int16))
+                assert (out[:do] == 7).all() and (out[do + n:] == 7).all()
+                assert int(flag.item()) == int(pos is not None), (n, so, do, bad)
+
+
+def test_engine_step_skips_on_overflow_seen_in_backward():
+    from patrickstar_b200 import initialize_engine
+    engine, opt = initialize_engine(model_func, 0, CONFIG)
+    x = torch.randn(8, 32, device=DEV, dtype=torch.float16)
+    before = [client_p.clone() for client_p in engine.client.chunk_state(0)]
+    out = engine(x)
+    loss = out.float().sum() * float("inf")      # every gradient becomes inf / nan
+    engine.backward(loss)
+    engine.step()                                 # no second scan: the flag came from the hand-off
+    assert opt.skipped_steps == 1 and opt.step_count == 0
+    assert engine.loss_scaler.loss_scale == 512
+    for a, b in zip(before, engine.client.chunk_state(0)):
+        assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+    # the skipped step restored the fp16 params from the master
+    for name, p in engine.module.named_parameters():
+        assert torch.isfinite(p).all()
+    out = engine(x)
+    engine.backward(out.float().pow(2).mean())
+    engine.step()
+    assert opt.step_count == 1 and opt.skipped_steps == 1
