@@ -32,8 +32,10 @@ def main():
                          symmetric=(SCAN in ("fused", "p2p")))
     client.append_tensor_list([("w%d" % i, cs - (7 if i == n_tensors - 1 else 0), i % 2)
                                for i in range(n_tensors)])
-    client.allocate()
+    n_off = int(os.environ.get("PS_TEST_OFFLOAD", "0"))     # local chunks kept in pinned host memory
+    client.allocate(state_budget_bytes=None if n_off == 0 else (4 - n_off) * 12 * cs)
     lay = client.layout
+    assert len(client.local_ids) == 4 and client.n_resident == 4 - n_off
     assert lay.n_chunks % world == 0 and client.rank == rank
     g0 = [p for n, p in client.params.items() if lay.tensor(n).group == 0]
     g1 = [p for n, p in client.params.items() if lay.tensor(n).group == 1]

@@ -26,3 +26,21 @@ def test_chunk_step_with_collectives(world, scan):
         err = "\n".join(ln for ln in (r.stdout + r.stderr).splitlines() if "Warning" not in ln)
         raise AssertionError(err[-6000:])
     assert "dist_worker ok" in r.stdout
+
+
+@pytest.mark.parametrize("scan", ["local", "reduced"])
+def test_chunk_step_with_collectives_and_offloaded_chunks(scan):
+    """Hybrid placement on several GPUs: two of each rank's four chunks keep their
+    fp32 state in pinned host memory and are streamed around the kernel between
+    their reduce-scatter and their all-gather."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    env = dict(os.environ, PS_TEST_SCAN=scan, PS_TEST_OFFLOAD="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", "29731", os.path.join(ROOT, "tests", "dist_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    if r.returncode != 0:
+        err = "\n".join(ln for ln in (r.stdout + r.stderr).splitlines() if "Warning" not in ln)
+        raise AssertionError(err[-6000:])
+    assert "dist_worker ok" in r.stdout
