@@ -563,13 +563,19 @@ def run_offload(args):
     the offloaded part measured alone (host->device copies, kernel, device->host copies)
     and overlap efficiency = max(component) / (step time - resident-only time)."""
     import torch
+    import torch.distributed as dist
     from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
     from patrickstar_b200.offload import OffloadPipeline
-    dev = torch.device("cuda", 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     cs, npr, k_off = args.chunk_size, args.chunks, args.offload_chunks
-    client = ChunkClient(rank=0, default_chunk_size=cs, world_size=1, device=dev, pack="flat")
-    client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr)])
+    client = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat")
+    client.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
     client.allocate(state_budget_bytes=(npr - k_off) * 12 * cs)
     assert len(client.local_ids) - client.n_resident == k_off
     scaler = DynamicLossScaler(device=dev, **SCALER)
@@ -577,7 +583,7 @@ def run_offload(args):
     if args.offload_slots != 2 or args.offload_piece != 16 * 1024 * 1024:
         opt._desc_host = opt._desc_host[:npr].copy()
         opt._offload = OffloadPipeline(client, opt, n_slots=args.offload_slots, piece_elems=args.offload_piece)
-    gen = torch.Generator(device=dev).manual_seed(1000)
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     tmp = torch.empty(cs, device=dev)
     for k in range(npr):
         for t, (mu, sd) in zip(client.chunk_state(k), ((0, 0.02), (0, 1e-4), (0, 1e-6))):
@@ -586,13 +592,21 @@ def run_offload(args):
     pristine = tmp.normal_(0, 8e-3, generator=gen).half()
 
     def refresh():
-        for c in range(npr):
+        for c in range(npr * world):
             client.fp16_chunk(c).copy_(pristine)
+
+    def step_fn():
+        if world > 1:
+            opt.step_with_collectives()
+        else:
+            opt.step()
 
     def timed(fn, n):
         ev = []
         for _ in range(n):
             refresh()
+            if world > 1:
+                dist.barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -603,10 +617,19 @@ def run_offload(args):
 
     for _ in range(args.warmup):
         refresh()
-        opt.step()
+        step_fn()
     torch.cuda.synchronize()
-    step_ms = timed(opt.step, args.steps)
-    # components of the offloaded part, each alone on one stream
+
+    def over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    step_ms = over_ranks(timed(step_fn, args.steps))
+    # components of the offloaded part, each alone on one stream (all ranks at once when N > 1,
+    # so that contention for the host's memory and PCIe switches shows)
     staging = [torch.empty(cs, dtype=torch.float32, device=dev) for _ in range(3)]
     off = range(client.n_resident, npr)
 
@@ -620,24 +643,33 @@ def run_offload(args):
             for src, dst in zip(staging, client.chunk_state(k)):
                 dst.copy_(src, non_blocking=True)
 
-    h2d_ms, d2h_ms = timed(h2d, 3), timed(d2h, 3)
-    # resident-only step time (same launch sequence without the pipeline)
+    h2d_ms, d2h_ms = over_ranks(timed(h2d, 3)), over_ranks(timed(d2h, 3))
+    # the same step without the pipeline (resident chunks and, for N > 1, all collectives)
     pipe, opt._offload = opt._offload, None
-    resident_ms = timed(opt.step, 3)
+    n_res_saved = client.n_resident
+    resident_ms = over_ranks(timed(step_fn, 3)) if world == 1 else None
     opt._offload = pipe
+    client.n_resident = n_res_saved
     kern_ms = k_off * (BYTES_PER_PARAM * cs / 6.2e12) * 1e3  # from the measured 6.2 TB/s of the step kernel
     bound = max(h2d_ms, d2h_ms, kern_ms)
-    line = {"workload": "hybrid offload: %d chunks x %d elements, %d resident in HBM, %d in pinned host memory, "
-                        "%d staging slots of %d elements" % (npr, cs, npr - k_off, k_off, args.offload_slots,
-                                                              opt._offload.piece_elems),
-            "metric": METRIC, "unit": UNIT, "value": npr * cs / (step_ms * 1e-3), "ms_per_step": step_ms,
-            "offloaded_params_per_s": k_off * cs / ((step_ms - resident_ms) * 1e-3),
-            "h2d_ms_alone": h2d_ms, "d2h_ms_alone": d2h_ms, "kernel_ms_offloaded_est": kern_ms,
-            "resident_only_ms": resident_ms,
-            "h2d_gbs": 12 * k_off * cs / (h2d_ms * 1e-3) / 1e9, "d2h_gbs": 12 * k_off * cs / (d2h_ms * 1e-3) / 1e9,
-            "overlap_efficiency": bound / (step_ms - resident_ms),
-            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
-    print(json.dumps(line))
+    pipe_ms = step_ms - resident_ms if resident_ms is not None else step_ms
+    if rank == 0:
+        line = {"workload": "hybrid offload: %d chunks x %d elements per rank, %d resident in HBM, %d in pinned "
+                            "host memory, %d staging slots of %d elements" % (
+                                npr, cs, npr - k_off, k_off, args.offload_slots, opt._offload.piece_elems),
+                "metric": METRIC, "unit": UNIT, "value": world * npr * cs / (step_ms * 1e-3),
+                "ms_per_step": step_ms, "offloaded_params_per_s_per_gpu": k_off * cs / (pipe_ms * 1e-3),
+                "h2d_ms_alone": h2d_ms, "d2h_ms_alone": d2h_ms, "kernel_ms_offloaded_est": kern_ms,
+                "resident_only_ms": resident_ms,
+                "h2d_gbs_per_gpu": 12 * k_off * cs / (h2d_ms * 1e-3) / 1e9,
+                "d2h_gbs_per_gpu": 12 * k_off * cs / (d2h_ms * 1e-3) / 1e9,
+                "overlap_efficiency": bound / pipe_ms,
+                "overlap_efficiency_note": "max(component alone) / (step - resident-only step); for N > 1 the "
+                                           "denominator is the whole step, collectives included",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
