@@ -101,3 +101,57 @@ def test_gpt2_xl_layout_counts():
     assert groups == {0, 1}
     n_decay = sum(int(np.prod(s)) for _, s, g in specs if g == 0)
     assert n_decay == 48 * (1600 * 4800 + 1600 * 1600 + 1600 * 6400 + 6400 * 1600) + 50257 * 1600 + 1024 * 1600
+
+
+def test_random_layouts_cover_every_element_once():
+    """Property test over random tensor lists, chunk sizes, packings and world
+    sizes: segments tile exactly the elements of the tensors (no overlap, no
+    hole inside a tensor), every chunk has one owner, the per-rank tables list
+    exactly the rank's segments, and slot 0 marks exactly the first piece."""
+    rng = np.random.RandomState(1234)
+    for trial in range(60):
+        cs = int(rng.choice([64, 100, 257, 1024]))
+        world = int(rng.choice([1, 2, 3, 4, 8]))
+        pack = str(rng.choice(["flat", "no_split"]))
+        lay = ChunkLayout(cs, world, pack)
+        n_t = int(rng.randint(1, 25))
+        total = 0
+        for i in range(n_t):
+            hi = cs if pack == "no_split" else 3 * cs
+            numel = int(rng.randint(1, hi + 1))
+            lay.append_tensor("t%d" % i, numel, int(rng.randint(0, 3)))
+            total += numel
+        lay.freeze()
+        assert lay.total_numel() == total
+        assert lay.n_chunks % world == 0 and lay.n_chunks >= lay.n_data_chunks
+        cover = np.zeros(lay.n_chunks * cs, dtype=np.int32)
+        group_at = np.full(lay.n_chunks * cs, -1, dtype=np.int32)
+        for t in lay.tensors:
+            s = t.flat_start(cs)
+            if pack == "no_split":
+                assert t.start_offset + t.numel <= cs          # never straddles
+            group_at[s:s + t.numel] = t.group
+        seen_chunks = []
+        for r in range(world):
+            local, numels, ranges, segs = lay.build_tables(r)
+            seen_chunks += local
+            first_slots = 0
+            for k, c in enumerate(local):
+                assert numels[k] == lay.chunk_numel(c) <= cs
+                prev = 0
+                for row in segs[ranges[k][0]:ranges[k][1]]:
+                    a, b, slot = int(row[0]), int(row[1]), int(row[2])
+                    assert prev <= a < b <= numels[k]
+                    prev = b
+                    cover[c * cs + a:c * cs + b] += 1
+                    g = group_at[c * cs + a:c * cs + b]
+                    assert (g == g[0]).all() and g[0] >= 0
+                    if slot == 0:
+                        first_slots += 1
+                    else:
+                        assert slot == 1 + g[0]
+            calls = lay.calls_of_rank(r)
+            assert first_slots == (1 if calls else 0)
+            assert lay.plan_groups(r)[2] == len(calls)
+        assert sorted(seen_chunks) == list(range(lay.n_chunks))
+        assert (cover[group_at >= 0] == 1).all() and (cover[group_at < 0] == 0).all()
