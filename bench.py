@@ -96,7 +96,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -380,15 +380,17 @@ def run_ours(args):
         finally:
             opt._update_resident = orig
 
+    # clocks are sampled from the warm-up on (the GPU is under the same load there), so that
+    # a timed region of a few hundred milliseconds still yields several samples
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         refresh_grads()
         one_step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
     launches0 = _lib.launch_count()
     step_ev = []
     torch.cuda.synchronize()

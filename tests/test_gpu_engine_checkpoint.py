@@ -123,6 +123,12 @@ def test_optimizer_checkpoint_round_trip():
             master = [ca.chunk_state(k)[0].clone() for k in range(2)]
     assert set(sd["state"][0]) >= {"step", "exp_avg", "exp_avg_sq", "betas", "lr", "weight_decay", "eps"}
     assert sd["state"][0]["exp_avg"].shape == (3000,) and sd["state"][0]["step"] == 5  # one of 6 skipped
+    # through the on-disk format the reference uses for it (torch.save of the dict)
+    import io
+    buf = io.BytesIO()
+    torch.save(sd, buf)
+    buf.seek(0)
+    sd = torch.load(buf, weights_only=False)
     cb, sb, ob = build()
     for k in range(2):
         cb.chunk_state(k)[0].copy_(master[k])
