@@ -42,7 +42,7 @@ NCU_DRAM_BYTES_PER_PARAM = 3.702e9 / (2 * 64 * 1024 * 1024)
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=CHUNKS_PER_RANK, help="chunks per rank")
@@ -96,7 +96,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "50"],
+                 "--format=csv,noheader,nounits", "-lms", "200"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -105,7 +105,16 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def wait_first_sample(self, timeout=5.0):
+        """nvidia-smi needs a few hundred milliseconds to start; wait for its first line."""
+        t_end = time.time() + timeout
+        while self.proc is not None and not self.lines and time.time() < t_end:
+            time.sleep(0.02)
+
+    def mark_load_begin(self):
+        self.t_load = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -117,7 +126,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        t_load = getattr(self, "t_load", 0.0)
+        under_load = [ln for ts, ln in self.lines if ts >= t_load]
+        for ln in (under_load or [ln for _, ln in self.lines]):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -385,6 +396,11 @@ def run_ours(args):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+        sampler.wait_first_sample()
+    if world > 1:
+        dist.barrier()
+    if sampler:
+        sampler.mark_load_begin()
     for _ in range(args.warmup):
         refresh_grads()
         one_step()
@@ -407,15 +423,27 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
     launches = _lib.launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
     step_ms = [a.elapsed_time(b) for a, b in step_ev]
     total_ms = sum(step_ms)
     if world > 1:
         t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
+    # A timed region shorter than about a second holds one or two nvidia-smi samples.  In that
+    # case keep the same load going (untimed, same steps) so that the median SM clock under
+    # this load rests on several samples; the sampler runs through the timed region as well.
+    n_extra = 0
+    if total_ms < 1000.0:
+        n_extra = max(1, min(400, int((1000.0 - total_ms) / max(total_ms / args.steps + 1.0, 1.0))))
+    for _ in range(n_extra):
+        refresh_grads()
+        one_step()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        clocks["untimed_tail_steps"] = n_extra  # samples taken under the same load after the timed steps
     ctrl = opt.read_ctrl()
-    assert ctrl.step == args.warmup + args.steps and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
+    assert ctrl.step == args.warmup + args.steps + n_extra and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
     params_per_step = npr * cs * world
     value = params_per_step * args.steps / (total_ms * 1e-3)
 

@@ -125,7 +125,9 @@ typedef struct ps_hyper_slot {
     float clip;         /* already min(65504, clip * scale); <= 0 disabled */
     float grad_divisor; /* <= 1 disabled */
     int32_t adamw_mode;
-    int32_t reserved[3];
+    float inv_loss_scale; /* 1 / loss_scale when the scale is a power of two (the product is then
+                             bit-identical to the division), else 0 = divide */
+    int32_t reserved[2];
 } ps_hyper_slot;
 
 /* Device-resident control block of one optimizer (one per FP16Adam object). */

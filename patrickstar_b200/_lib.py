@@ -68,7 +68,7 @@ class HyperSlot(C.Structure):
                 ("beta1_minus1", C.c_float), ("beta2_minus1", C.c_float), ("bias2_sqrt", C.c_float),
                 ("eps", C.c_float), ("step_size", C.c_float), ("weight_decay", C.c_float),
                 ("w_decay", C.c_float), ("clip", C.c_float), ("grad_divisor", C.c_float),
-                ("adamw_mode", C.c_int32), ("reserved", C.c_int32 * 3)]
+                ("adamw_mode", C.c_int32), ("inv_loss_scale", C.c_float), ("reserved", C.c_int32 * 2)]
 
 
 class StepCtrl(C.Structure):

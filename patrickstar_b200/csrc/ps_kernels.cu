@@ -94,6 +94,7 @@ struct Slot {
     float loss_scale, beta1, beta2, b1m1, b2m1, bias2_sqrt, eps, step_size, wd, w_decay, clip,
         divisor;
     int adamw;
+    float inv_scale;  // 1 / loss_scale when that is exact (power-of-two scale), else 0
 };
 
 __device__ __forceinline__ Slot load_slot(const ps_hyper_slot* s)
@@ -116,6 +117,7 @@ __device__ __forceinline__ Slot load_slot(const ps_hyper_slot* s)
     r.clip = __uint_as_float(c.z);
     r.divisor = __uint_as_float(c.w);
     r.adamw = (int)d.x;
+    r.inv_scale = __uint_as_float(d.y);
     return r;
 }
 
@@ -135,6 +137,7 @@ __device__ __forceinline__ Slot slot_from_value(const ps_hyper_slot& s)
     r.clip = s.clip;
     r.divisor = s.grad_divisor;
     r.adamw = s.adamw_mode;
+    r.inv_scale = s.inv_loss_scale;
     return r;
 }
 
@@ -158,10 +161,27 @@ __device__ __forceinline__ float grad_from_half(uint32_t h, const Slot& s)
     return g;
 }
 
+// 1 / scale when scale is a positive power of two whose reciprocal is a normal float, else 0.
+__host__ __device__ __forceinline__ float exact_reciprocal_or_zero(float scale)
+{
+    union { float f; uint32_t u; } a, r;
+    a.f = scale;
+    const uint32_t e = (a.u >> 23) & 0xffu;
+    if ((a.u & 0x807fffffu) != 0u || e == 0u || e > 253u) return 0.f;
+    r.u = (254u - e) << 23;
+    return r.f;
+}
+
 // One element of Adam_Optimizer::Step's SIMD body (cpu_adam.cpp:91-143).
 __device__ __forceinline__ void adam_element(float g, float& p, float& m, float& v, const Slot& s)
 {
-    if (s.loss_scale > 0.f) g = __fdiv_rn(g, s.loss_scale);
+    // g / scale.  For a power-of-two scale the product with the exact reciprocal is the same
+    // correctly rounded value (both round the same real number), and costs one instruction
+    // instead of a division sequence.
+    if (s.inv_scale != 0.f)
+        g = __fmul_rn(g, s.inv_scale);
+    else if (s.loss_scale > 0.f)
+        g = __fdiv_rn(g, s.loss_scale);
     if (s.wd > 0.f && !s.adamw) g = __fmaf_rn(p, s.wd, g);
     m = __fmul_rn(m, s.beta1);
     m = __fmaf_rn(g, s.b1m1, m);
@@ -1011,7 +1031,8 @@ __device__ void derive_slot(ps_hyper_slot* out, const ps_group_hyper& g, float b
     out->clip = clip;
     out->grad_divisor = divisor;
     out->adamw_mode = g.adamw_mode;
-    out->reserved[0] = out->reserved[1] = out->reserved[2] = 0;
+    out->inv_loss_scale = loss_scale > 0.f ? exact_reciprocal_or_zero(loss_scale) : 0.f;
+    out->reserved[0] = out->reserved[1] = 0;
 }
 
 __device__ void pow_lookup(const float* tab, uint64_t tab_len, int group, uint64_t t, float beta1,
@@ -1224,6 +1245,7 @@ struct AdamClock {
         s.clip = 0.f;
         s.grad_divisor = 0.f;
         s.adamw_mode = adamw_mode ? 1 : 0;
+        s.inv_loss_scale = loss_scale > 0.f ? exact_reciprocal_or_zero(loss_scale) : 0.f;
         return s;
     }
 };
