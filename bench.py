@@ -595,7 +595,6 @@ def run_offload(args):
     import torch
     import torch.distributed as dist
     from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
-    from patrickstar_b200.offload import OffloadPipeline
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -611,8 +610,7 @@ def run_offload(args):
     scaler = DynamicLossScaler(device=dev, **SCALER)
     opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
     if args.offload_slots != 2 or args.offload_piece != 16 * 1024 * 1024:
-        opt._desc_host = opt._desc_host[:npr].copy()
-        opt._offload = OffloadPipeline(client, opt, n_slots=args.offload_slots, piece_elems=args.offload_piece)
+        opt.configure_offload(n_slots=args.offload_slots, piece_elems=args.offload_piece)
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     tmp = torch.empty(cs, device=dev)
     for k in range(npr):

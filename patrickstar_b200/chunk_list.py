@@ -79,6 +79,8 @@ class ChunkLayout:
         self._n_chunks = 0          # chunks holding tensors
         self._fill = 0              # used elements of the last chunk
         self._frozen = False
+        self._piece_cache = None    # filled once the layout is frozen
+        self._by_chunk = None
 
     # ------------------------------------------------------------------ packing
     def append_tensor_list(self, specs: Sequence[Tuple[str, int, int]], shapes=None):
@@ -138,6 +140,13 @@ class ChunkLayout:
     def freeze(self):
         self._frozen = True
         return self
+
+    def set_group(self, name, group):
+        """Re-assign a tensor's hyper-parameter group (the optimizer's param groups
+        decide it) and drop the cached segment lists."""
+        self._by_name[name].group = int(group)
+        self._piece_cache = None
+        self._by_chunk = None
 
     # ---------------------------------------------------------------- geometry
     @property

@@ -64,6 +64,7 @@ class ChunkClient:
         self.p32_host = self.exp_avg_host = self.exp_avg_sq_host = None  # offloaded local chunks
         self.n_resident = 0
         self.local_ids = []
+        self._pending = []    # (name, nn.Parameter) registered from a module, placed at allocate()
 
     # ------------------------------------------------------------- registration
     def append_tensor_list(self, specs, shapes=None):
@@ -77,7 +78,6 @@ class ChunkClient:
         sub-module as the reference's pre-process context does
         (patrickstar/core/preprocess.py:341-435).  ``group_of(name, param)``
         gives the hyper-parameter group index (default 0)."""
-        self._pending = []
         for mod_name, mod in module.named_modules():
             specs, shapes, plist = [], [], []
             for pname, p in mod.named_parameters(recurse=False):
@@ -138,18 +138,18 @@ class ChunkClient:
         self.p32, self.exp_avg, self.exp_avg_sq = dev_buf(), dev_buf(), dev_buf()
         self.p32_host, self.exp_avg_host, self.exp_avg_sq_host = host_buf(), host_buf(), host_buf()
         # parameters registered from a module: move their values into the chunks
-        for full, p in getattr(self, "_pending", []):
+        for full, p in self._pending:
             info = lay.tensor(full)
             view = self.fp16_view(info)
             view.copy_(p.detach().to(device=dev, dtype=torch.float16).reshape(-1))
             p.data = view.view(p.shape)
             self.params[full] = p
-        if not getattr(self, "_pending", None):
+        if not self._pending:
             # tensors registered by shape only: parameters are views of the fp16 buffer
             for info in lay.tensors:
                 view = self.fp16_view(info).view(info.shape)
                 self.params[info.name] = torch.nn.Parameter(view, requires_grad=False)
-        if init_master_from_fp16 and getattr(self, "_pending", None):
+        if init_master_from_fp16 and self._pending:
             for k, c in enumerate(self.local_ids):
                 self.chunk_state(k)[0].copy_(self.fp16_chunk(c).float())
         self._pending = []

@@ -92,9 +92,7 @@ class FP16Adam(torch.optim.Optimizer):
                 st["weight_decay"] = group["weight_decay"]
                 st["eps"] = group["eps"]
                 st["name"] = name_of[id(p)]
-                lay.tensor(name_of[id(p)]).group = gi
-        lay._piece_cache = None
-        lay._by_chunk = None
+                lay.set_group(name_of[id(p)], gi)
 
         # section timing of the step on CUDA events (off by default; no sync either way)
         self.time_profile = False
@@ -111,6 +109,16 @@ class FP16Adam(torch.optim.Optimizer):
         if client.n_resident < len(client.local_ids):
             from .offload import OffloadPipeline
             self._offload = OffloadPipeline(client, self)
+
+    def configure_offload(self, n_slots=2, piece_elems=16 * 1024 * 1024):
+        """Rebuild the offload pipeline with another number of staging slots or
+        another piece size (no-op when every local chunk is resident)."""
+        if self.client.n_resident >= len(self.client.local_ids):
+            return
+        from .offload import OffloadPipeline
+        self._offload = None
+        self._desc_host = self._desc_host[:self._n_local].copy()
+        self._offload = OffloadPipeline(self.client, self, n_slots=n_slots, piece_elems=piece_elems)
 
     # ------------------------------------------------------------------ tables
     def _stream(self):

@@ -29,9 +29,7 @@ def test_offloaded_chunks_match_oracle(n_resident, piece):
                    loss_scaler=scaler, lr=1e-3, eps=1e-6, use_adamw=True)
     assert (opt._offload is not None) == (n_resident < n_local)
     if opt._offload is not None:
-        from patrickstar_b200.offload import OffloadPipeline
-        opt._desc_host = opt._desc_host[:n_local].copy()
-        opt._offload = OffloadPipeline(client, opt, n_slots=2, piece_elems=piece)
+        opt.configure_offload(n_slots=2, piece_elems=piece)
     P, M, V = fill_states(client, 21)
     so = DynamicScalerOracle(8, 2, 1000, 1)
     orc = StepOracle(oracle_calls(client), groups_of(opt), so, True)
@@ -53,12 +51,10 @@ def test_offloaded_chunks_match_oracle(n_resident, piece):
 
 def test_more_slots_than_chunks_and_three_slots():
     from patrickstar_b200 import FP16Adam, LossScaler
-    from patrickstar_b200.offload import OffloadPipeline
     cs = 8192
     client = make_client([("w%d" % i, cs, 0) for i in range(5)], cs, budget=0)
     opt = FP16Adam(client, client.params.values(), loss_scaler=LossScaler(4.0), lr=1e-3)
-    opt._desc_host = opt._desc_host[:len(client.local_ids)].copy()
-    opt._offload = OffloadPipeline(client, opt, n_slots=3, piece_elems=4096)
+    opt.configure_offload(n_slots=3, piece_elems=4096)
     P, M, V = fill_states(client, 31)
     from oracle.scaler_oracle import StaticScalerOracle
     orc = StepOracle(oracle_calls(client), groups_of(opt), StaticScalerOracle(4.0), False)
