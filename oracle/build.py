@@ -27,7 +27,9 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("PS_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: $PS_REFERENCE_ROOT, else a directory "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("PS_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 REF_CSRC = os.path.join(REFERENCE_ROOT, "patrickstar", "ops", "csrc")
 
 _SIMD = {

@@ -1,6 +1,7 @@
 """Generates the golden fixtures of tests/golden/ by RUNNING THE REFERENCE.
 
-Needs the reference checkout (PS_REFERENCE_ROOT, default /root/reference) and
+Needs the reference checkout (PS_REFERENCE_ROOT, default: a directory "reference"
+beside this repository) and
 the compiled reference module (``python oracle/build.py``).  Run from the
 repository root:  ``python tests/golden/make_golden.py``
 
@@ -25,7 +26,7 @@ sys.path.insert(0, ROOT)
 from oracle import ref  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_ROOT = os.environ.get("PS_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("PS_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def checksum(t):
