@@ -114,6 +114,10 @@ class ChunkStepEngine(torch.nn.Module):
         """optimizer.step() without a second overflow scan when every gradient came
         through ``backward`` above."""
         scanned, self._grads_scanned = getattr(self, "_grads_scanned", False), False
+        if self.client.world_size > 1:
+            # data parallel: reduce-scatter of the gradient chunks, rank-local step,
+            # all-gather of the param chunks (patrickstar/core/client.py:818-856, 428-497)
+            return self.optimizer.step_with_collectives(scan="done" if scanned else "local")
         return self.optimizer.step(scan=not scanned)
 
 

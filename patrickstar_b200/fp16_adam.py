@@ -336,23 +336,28 @@ class FP16Adam(torch.optim.Optimizer):
         group g-1 are in flight together (two communicators, events between
         streams, no host synchronisation).
 
+        ``scan="done"`` is ``"local"`` for a caller whose gradients were already
+        tested when they were handed over (``handoff_grad``): only the flag
+        all-reduce remains.
+
         ``scan="reduced"`` tests the reduced gradients instead (additionally
         catches an fp16 overflow created by the sum itself); every
         reduce-scatter must then finish before the first update."""
         c = self.client
         if c.world_size == 1:
             return self.step()
-        if scan not in ("local", "reduced"):
-            raise ValueError("scan must be 'local' or 'reduced'")
+        if scan not in ("local", "reduced", "done"):
+            raise ValueError("scan must be 'local', 'reduced' or 'done'")
         lay = c.layout
         n_groups = lay.n_groups_comm
         item = CHUNK_DESC_DTYPE.itemsize
         with torch.cuda.device(self.device):
             st = self._stream()
-            if scan == "local":
+            if scan in ("local", "done"):
                 if self._dynamic:
-                    check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(),
-                                                      self._scaler.flag_ptr, st), "ps_overflow_scan_buffer")
+                    if scan == "local":
+                        check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(),
+                                                          self._scaler.flag_ptr, st), "ps_overflow_scan_buffer")
                     c.all_reduce_flag(self._scaler.flag_tensor)
                 self._begin(c.world_size, st)
             rs = [c.reduce_scatter_group(g, async_op=True) for g in range(n_groups)]
@@ -368,7 +373,7 @@ class FP16Adam(torch.optim.Optimizer):
             ag = []
             n_res = c.n_resident   # local chunk k belongs to communication group k
             for g in range(min(n_res, n_groups)):
-                if scan == "local":
+                if scan != "reduced":
                     rs[g].wait()
                 self._update_resident(st, first=g, count=1)
                 ag.append(c.all_gather_group(g, async_op=True))
@@ -377,7 +382,7 @@ class FP16Adam(torch.optim.Optimizer):
                 # pinned host memory go through the offload pipeline once their reduced
                 # gradients are in, and are gathered when it has drained (PCIe, at 14 ms
                 # per chunk, dwarfs the 1-2 ms of their all-gathers)
-                if scan == "local":
+                if scan != "reduced":
                     for g in range(n_res, n_groups):
                         rs[g].wait()
                 self._offload.run()

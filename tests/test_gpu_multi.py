@@ -48,3 +48,19 @@ def test_chunk_step_with_collectives_and_offloaded_chunks(scan):
         err = "\n".join(ln for ln in (r.stdout + r.stderr).splitlines() if "Warning" not in ln)
         raise AssertionError(err[-6000:])
     assert "dist_worker ok" in r.stdout
+
+
+def test_data_parallel_engine_end_to_end():
+    """initialize_engine on 2 ranks with different batches: forward, scaled backward
+    with the gradient hand-off, step with the chunk collectives; ranks stay in sync,
+    an overflow on one rank skips the step on both, the loss goes down."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", "29741", os.path.join(ROOT, "tests", "dist_engine_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    if r.returncode != 0:
+        err = "\n".join(ln for ln in (r.stdout + r.stderr).splitlines() if "Warning" not in ln)
+        raise AssertionError(err[-6000:])
+    assert "dist_engine_worker ok" in r.stdout
