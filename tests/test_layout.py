@@ -155,3 +155,24 @@ def test_random_layouts_cover_every_element_once():
             assert lay.plan_groups(r)[2] == len(calls)
         assert sorted(seen_chunks) == list(range(lay.n_chunks))
         assert (cover[group_at >= 0] == 1).all() and (cover[group_at < 0] == 0).all()
+
+
+@pytest.mark.parametrize("name,chunks,per_rank_at_8", [("gpt_12b", 192, 24), ("gpt_40b", 583, 73)])
+def test_large_gpt_layouts_and_ownership(name, chunks, per_rank_at_8):
+    """The 12B (40 layers, hidden 5120) and 40B (48 layers, hidden 8192) GPT
+    configurations cut into 64 Mi-element chunks: single tensors exceed a chunk
+    (flat packing is required), chunk counts and the per-rank share on 8 ranks."""
+    from patrickstar_b200.model_layouts import model_specs
+    specs = model_specs(name)
+    cs = 64 * 1024 * 1024
+    assert max(int(np.prod(s)) for _, s, _ in specs) > cs
+    with pytest.raises(RuntimeError, match="larger than the chunk size"):
+        ChunkLayout(cs, 8, "no_split").append_tensor_list([(n, int(np.prod(s)), g) for n, s, g in specs])
+    lay = ChunkLayout(cs, 8, "flat")
+    lay.append_tensor_list([(n, int(np.prod(s)), g) for n, s, g in specs])
+    lay.freeze()
+    assert lay.n_data_chunks == chunks
+    assert lay.n_chunks == per_rank_at_8 * 8 and len(lay.local_chunk_ids(3)) == per_rank_at_8
+    # 12 B of fp32 state per parameter on the owner: the 40B model needs the offload tier under a 40 GB budget
+    state_gib = per_rank_at_8 * 12 * cs / 2 ** 30
+    assert (state_gib > 40) == (name == "gpt_40b")
