@@ -60,6 +60,11 @@ def parse_args():
                          "'fused' = one kernel over NVSwitch multicast memory (multimem); 'p2p' = one kernel "
                          "over peer loads / stores; 'auto' = p2p for 2-3 ranks, fused for more, nccl if "
                          "symmetric memory cannot be set up")
+    ap.add_argument("--layout", default="uniform", choices=["uniform", "gpt2_1.5b"],
+                    help="N = 1 only: 'gpt2_1.5b' packs the GPT-2 1.5B tensors flat into 64 Mi chunks (24 "
+                         "chunks, ~580 tensors, AdamW with two param groups straddling chunk boundaries) "
+                         "instead of the uniform one-tensor-per-chunk workload; a side measurement of what "
+                         "the segment tables cost")
     ap.add_argument("--offload-chunks", type=int, default=0,
                     help="keep the fp32 state of this many of the rank's chunks in pinned host memory and "
                          "stream them through the double-buffered offload pipeline (hybrid placement); "
@@ -315,10 +320,20 @@ def run_ours(args):
         args.collectives = "nccl" if world == 1 else ("p2p" if world <= 3 else "fused")
     fused = world > 1 and args.collectives in ("fused", "p2p")
 
+    gpt_layout = args.layout != "uniform"
+    if gpt_layout and world != 1:
+        raise SystemExit("--layout %s is a single-GPU side measurement" % args.layout)
+
     def make_client(symmetric):
         c = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
                         symmetric=symmetric)
-        c.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
+        if gpt_layout:
+            from patrickstar_b200.model_layouts import model_specs
+            import numpy as np
+            specs = model_specs(args.layout)
+            c.append_tensor_list([(n, int(np.prod(sh)), g) for n, sh, g in specs])
+        else:
+            c.append_tensor_list([("chunk%d" % i, cs, 0) for i in range(npr * world)])
         c.allocate()
         return c
 
@@ -341,7 +356,16 @@ def run_ours(args):
     else:
         client = make_client(False)
     scaler = DynamicLossScaler(device=dev, **SCALER)
-    opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
+    if gpt_layout:
+        npr = args.chunks = len(client.local_ids)
+        lay = client.layout
+        decay = [p for n, p in client.params.items() if lay.tensor(n).group == 0]
+        no_decay = [p for n, p in client.params.items() if lay.tensor(n).group == 1]
+        hyper = dict(HYPER, weight_decay=0.01)
+        opt = FP16Adam(client, [{"params": decay}, {"params": no_decay, "weight_decay": 0.0}],
+                       loss_scaler=scaler, use_adamw=True, **hyper)
+    else:
+        opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, use_adamw=False, **HYPER)
 
     # seeded synthetic state, generated on the device chunk by chunk
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -444,7 +468,7 @@ def run_ours(args):
         clocks["untimed_tail_steps"] = n_extra  # samples taken under the same load after the timed steps
     ctrl = opt.read_ctrl()
     assert ctrl.step == args.warmup + args.steps + n_extra and ctrl.n_skipped == 0, (ctrl.step, ctrl.n_skipped)
-    params_per_step = npr * cs * world
+    params_per_step = opt.params_per_step if gpt_layout else npr * cs * world
     value = params_per_step * args.steps / (total_ms * 1e-3)
 
     peak, peak_kind = measured_peaks()
@@ -463,7 +487,8 @@ def run_ours(args):
         kern_ms = [a.elapsed_time(b) for a, b, _ in kernel_ev]
         kern_chunks = sum(c for _, _, c in kernel_ev)
         kern_avg_ms = sum(kern_ms) / len(kern_ms)
-        bytes_per_launch = BYTES_PER_PARAM * cs * (kern_chunks / len(kernel_ev))
+        bytes_per_launch = (BYTES_PER_PARAM * params_per_step if gpt_layout
+                            else BYTES_PER_PARAM * cs * (kern_chunks / len(kernel_ev)))
         achieved = bytes_per_launch / (kern_avg_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "chunk_step_kernel", "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_source": "%s copy bandwidth" % peak_kind,
@@ -511,6 +536,10 @@ def run_ours(args):
             line["e2e"] = e2e
         if fallback_note:
             line["config"]["note"] = fallback_note
+        if gpt_layout:
+            line["config"]["workload"] = ("GPT-2 1.5B layout: %d parameters in %d chunks of %d elements, %d "
+                                          "segments, AdamW wd 0.01 / 0 in two param groups" % (
+                                              params_per_step, npr, cs, len(opt._segs_host)))
         if local_step is not None:
             line["local_step"] = local_step
             line["config"]["overflow_scan"] = "local" if fused else args.scan
