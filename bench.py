@@ -165,6 +165,19 @@ def _load_cpu_impl():
         return "port", port
 
 
+def use_all_host_threads():
+    """The CPU arms run on every core the process may use.  (torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its workers; the OpenMP runtime shared by torch and the compiled
+    reference follows torch.set_num_threads.)"""
+    import torch
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_chunk_inputs(n):
     import torch
     g = torch.Generator().manual_seed(0)
@@ -189,7 +202,7 @@ def cpu_baseline(n, seconds=10.0, max_calls=2000, warm=3):
     threads.  Bounded sample: 1 chunk, about `seconds` of calls."""
     import torch
     kind, impl = _load_cpu_impl()
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     p, m, v, g = cpu_chunk_inputs(n)
     if kind == "reference":
         impl.create_adam(31337, HYPER["lr"], HYPER["betas"][0], HYPER["betas"][1], HYPER["eps"],
@@ -226,7 +239,7 @@ def run_reference_arm(args):
         return
     kind, impl = _load_cpu_impl()
     n, nchunks = args.chunk_size, args.chunks
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     p0, m0, v0, g0 = cpu_chunk_inputs(n)
     # a bounded sample: `sample` chunks stand for the rank's `nchunks` (same distributions)
     sample = min(nchunks, 4)
