@@ -127,7 +127,10 @@ typedef struct ps_hyper_slot {
     int32_t adamw_mode;
     float inv_loss_scale; /* 1 / loss_scale when the scale is a power of two (the product is then
                              bit-identical to the division), else 0 = divide */
-    int32_t reserved[2];
+    float inv_grad_divisor; /* float(1 / grad_divisor): torch computes the fp16 `payload /= world_size`
+                               on a CUDA tensor as half(float(g) * (1.0f / world)); 0 = derive it in the
+                               kernel */
+    int32_t reserved;
 } ps_hyper_slot;
 
 /* Device-resident control block of one optimizer (one per FP16Adam object). */
@@ -182,8 +185,9 @@ int ps_adam_get_state(int optimizer_id, float out[4], uint64_t* step);
 /* ------------------------------------------------------------------ */
 
 /* Host-side validation of a chunk table and its segment table before they are
- * uploaded: 16-byte aligned non-null bases, numel <= chunk_capacity, segments
- * sorted, non-overlapping, inside numel, slot < n_slots. */
+ * uploaded: 16-byte aligned non-null bases, numel <= chunk_capacity, `reserved`
+ * (first element) a multiple of 2048 and below numel (0 for an empty chunk),
+ * segments sorted, non-overlapping, inside numel, slot < n_slots. */
 int ps_table_check(const ps_chunk_desc* chunks_host, uint32_t n_chunks, const ps_segment* segs_host,
                    uint32_t n_segs, uint32_t n_slots, uint32_t chunk_capacity);
 
@@ -242,6 +246,44 @@ int ps_scaler_update(ps_scaler_state* scaler_dev, int32_t* flag_dev, int overflo
 int ps_chunk_step(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
                   const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, void* stream);
 
+/* FP16Adam.has_overflow_and_reset_param's restore alone
+ * (patrickstar/ops/fp16_cpu_adam.py:298-309): the fp16 slot of every segment of
+ * every chunk of the table := half(fp32 master), 6 B/element, without a control
+ * block.  (ps_chunk_step does the same when ctrl->skip is set.) */
+int ps_restore_fp16(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                    const ps_segment* segs_dev, void* stream);
+
+/* One parameter that is managed by torch instead of the chunk list — the
+ * reference's TORCH_BASED kind (the CPU-embedding weights,
+ * patrickstar/core/preprocess.py:351-369): the parameter itself is the fp32
+ * master, its gradient is fp32, there is no fp16 slot and no write-back
+ * (patrickstar/ops/fp16_cpu_adam.py:345-353).  All pointers need 4-byte
+ * alignment only; 16-byte aligned ones take a vector path. */
+typedef struct ps_tensor_desc {
+    float* p32;        /* the parameter, fp32, updated in place */
+    const float* grad; /* its fp32 gradient, read-only          */
+    float* exp_avg;
+    float* exp_avg_sq;
+    uint64_t numel;
+    uint32_t slot;     /* ps_hyper_slot of its call in the step's call sequence */
+    uint32_t reserved;
+} ps_tensor_desc;
+
+#define PS_TENSOR_TABLE_MAX 1024u /* rows per ps_tensor_table_step call */
+
+/* The step for a table of such parameters, one launch, driven by the same
+ * control block as ps_chunk_step: nothing happens when ctrl->skip is set (the
+ * reference neither tests these gradients for overflow nor restores these
+ * parameters, fp16_cpu_adam.py:301-302, 485-486); otherwise every element gets
+ * the update of ps_chunk_step with the gradient taken as fp32 (unscale by the
+ * slot's loss scale, fp32 clamp when clipping is on, no world-size division).
+ * 28 B/element.  The table is given in HOST memory, because the gradient
+ * pointers change every step; it is validated, copied (the caller may reuse it
+ * as soon as the call returns) and uploaded into table_dev, n_tensors rows of
+ * device memory owned by the caller.  No synchronisation. */
+int ps_tensor_table_step(const ps_tensor_desc* tensors_host, uint32_t n_tensors, uint32_t n_slots,
+                         ps_tensor_desc* table_dev, const ps_step_ctrl* ctrl_dev, void* stream);
+
 /* The multi-GPU chunk step as ONE kernel: the step of ps_chunk_step fused with
  * the reduce-scatter of the fp16 grad chunks before it
  * (patrickstar/core/client.py:818-856) and the all-gather of the fp16 param
@@ -272,6 +314,23 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
 int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
                       const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev, const void* fp16_local_base,
                       const uint64_t* peer_bases_dev, int world_size, void* stream);
+
+/* ps_chunk_step_fused as a two-stage pipeline over the same multicast memory,
+ * for measurements of how the NVLink round trip is best hidden: per owned chunk
+ * a light kernel on the pipeline's own stream pulls the switch-side sum of the
+ * gradients (multimem.ld_reduce) into one of two local staging buffers while
+ * the step kernel on `stream` updates the previous chunk from its staging
+ * buffer and stores the fp16 params to all ranks (multimem.st).  staging_dev:
+ * 2 * max_numel fp16 elements of plain device memory owned by the caller.
+ * Results are bit-identical to ps_chunk_step_fused.  ps_fused_pipe_create makes
+ * the stream and events (no device memory). */
+int ps_fused_pipe_create(void** pipe_out);
+int ps_fused_pipe_destroy(void* pipe);
+int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint32_t n_chunks,
+                               uint32_t max_numel, const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev,
+                               const void* fp16_local_base, const void* fp16_multicast_base,
+                               const uint64_t* peer_bases_dev, int world_size, uint16_t* staging_dev,
+                               void* stream);
 
 /* dst[i] = the reduced gradient ps_chunk_step_p2p loads for the element at
  * fp16_local_ptr + 2*i of this rank's buffer.  For tests. */
@@ -364,21 +423,32 @@ int ps_offload_last_cuda_error(void);
  *
  * Limits: n_chunks <= PS_STATIC_MAX_CHUNKS and n_segs <= PS_STATIC_MAX_SEGMENTS,
  * else PS_ERR_LIMIT and nothing is enqueued; larger jobs are split by the
- * caller.  The tables are validated like ps_table_check does.
+ * caller.  The tables are validated like ps_table_check does, and
+ * ps_chunk_desc.reserved must be 0 here (PS_ERR_TABLE otherwise).
  *
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
  * All calls share the one array and each call overwrites it completely:
  * calls on one stream are ordered and safe, calls that can overlap on the GPU
  * (different streams, different threads) race on it and must be serialised by
- * the caller.  The host tables may be reused as soon as the call returns. */
+ * the caller.
+ *
+ * The host tables and slots are copied, before the call returns, into a
+ * pageable host buffer the library keeps per calling thread, and uploaded from
+ * there; the caller's own tables — pageable, pinned or registered — may
+ * therefore be changed or freed as soon as the call returns. */
 int ps_chunk_step_static(const ps_chunk_desc* chunks_host, uint32_t n_chunks, uint32_t max_numel,
                          const ps_segment* segs_host, uint32_t n_segs,
                          const ps_hyper_slot* slots_host, uint32_t n_slots, int skip, void* stream);
 
 /* Tuning knobs for measurements: "unroll" (1, 2, 4: 128-bit groups per thread
  * per tile of the step kernels), "scan_unroll" (1, 2, 4), "blocks_per_sm"
- * (0 = occupancy calculator).  No counterpart in the reference. */
+ * (0 = occupancy calculator), "bulk" (0, or 2..4 stages of the bulk-async
+ * staged chunk step), "fused_depth" (2, 4, 8: reduced-gradient loads a thread
+ * of ps_chunk_step_fused keeps in flight), "fused_blocks_per_sm",
+ * "pull_blocks_per_sm" / "staged_blocks_per_sm" (grids of the two kernels of
+ * ps_chunk_step_fused_staged), "p2p_unroll" (0 = by world size, 1, 2),
+ * "p2p_blocks_per_sm".  No counterpart in the reference. */
 int ps_tune(const char* key, int value);
 
 /* Kernel launch counter: number of kernels this library has launched in this

@@ -198,9 +198,13 @@ int ps_oracle_has_inf_or_nan_f16(const uint16_t* g, size_t n)
  * by world_size in fp16: torch computes half(float(h) / float(world)). */
 void ps_oracle_div_world_f16(uint16_t* g, size_t n, int world_size)
 {
-    const float w = (float)world_size;
+    /* `payload /= world_size` on a CUDA fp16 tensor with a Python scalar: torch
+     * multiplies by the fp32 reciprocal of the scalar (its division kernel takes
+     * that route for a scalar divisor) and rounds the fp32 product to fp16.  For
+     * a power-of-two world size this is the true quotient. */
+    const float inv = 1.0f / (float)world_size;
 #pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; i++) g[i] = f2h(h2f(g[i]) / w);
+    for (size_t i = 0; i < n; i++) g[i] = f2h(h2f(g[i]) * inv);
 }
 
 /* fp16 SUM of `world` buffers the way a reduction with fp32 accumulation and a

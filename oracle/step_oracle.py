@@ -16,6 +16,12 @@ one rank's local chunks:
     (patrickstar/core/client.py:838) when ``world_size > 1`` and clamped in
     fp16 when gradient clipping is on (``:365-379``, GPU flavour).
 
+  * a torch-managed parameter (``:345-353``: fp32 parameter that is its own
+    master, fp32 gradient) is one more adam_update call at its place of the
+    visiting order, with no fp16 write-back; its gradient is neither divided by
+    the world size nor tested for overflow, and an overflow step leaves it
+    untouched (``:301-302``).
+
 Arrays are numpy: fp16 chunks as uint16/float16, states as float32.
 """
 import numpy as np
@@ -26,7 +32,9 @@ from . import port
 class StepOracle:
     def __init__(self, calls, groups, scaler, use_adamw, gradient_clipping=-1, world_size=1,
                  trailing_call_group=None):
-        """calls: list of (chunk_index, start, end, group) in visiting order.
+        """calls: list of (chunk_index, start, end, group) in visiting order; an
+        entry ("torch", k, group) is the k-th torch-managed parameter of the
+        ``torch_params`` list given to ``step``.
         groups: list of dicts lr / betas / eps / weight_decay.
         trailing_call_group: when the oracle follows only the first tensors of a
         rank, the group index of the rank's LAST tensor: an empty adam_update
@@ -59,9 +67,11 @@ class StepOracle:
             g = np.clip(g.astype(np.float32), -c, c).astype(np.float16)
         return g
 
-    def step(self, h16, p32, exp_avg, exp_avg_sq, overflow=None):
+    def step(self, h16, p32, exp_avg, exp_avg_sq, overflow=None, torch_params=None):
         """h16 / p32 / exp_avg / exp_avg_sq: lists of per-chunk arrays (in place).
-        overflow: the flag after the all-reduce; None = derive from h16."""
+        overflow: the flag after the all-reduce; None = derive from h16.
+        torch_params: list of (param fp32, grad fp32, exp_avg, exp_avg_sq) flat
+        arrays of the torch-managed parameters (updated in place)."""
         dynamic = self.scaler is not None and getattr(self.scaler, "dynamic", False)
         if overflow is None:
             overflow = dynamic and any(port.has_inf_or_nan_f16(h.view(np.uint16)) for h in h16)
@@ -71,7 +81,10 @@ class StepOracle:
             # every local parameter's fp16 slot := cast(fp32 master).  (The reference
             # copies chunk-wise, gaps included; gaps hold zeros on both sides there,
             # so restoring the parameters' own elements is the same thing.)
-            for (c, s, e, _) in self.calls:
+            for call in self.calls:
+                if call[0] == "torch":
+                    continue
+                c, s, e, _ = call
                 out = np.empty(e - s, dtype=np.uint16)
                 port.cast_fp32_to_fp16(np.ascontiguousarray(p32[c][s:e]), out)
                 h16[c].view(np.uint16)[s:e] = out
@@ -80,7 +93,20 @@ class StepOracle:
             return True
         self.step_count += 1
         loss_scale = self.scaler.loss_scale if self.scaler is not None else -1
-        for (c, s, e, g) in self.calls:
+        for call in self.calls:
+            if call[0] == "torch":
+                _, k, g = call
+                hp = self.groups[g]
+                tp, tg, tm, tv = torch_params[k]
+                if self.clip > 0:
+                    # clamp_ on the fp32 gradient itself (fp16_cpu_adam.py:365-379)
+                    c_ = self.clip * (self.scaler.loss_scale if self.scaler is not None else 1)
+                    c_ = np.float32(min(65504.0, c_))
+                    tg = np.clip(tg, -c_, c_).astype(np.float32)
+                self.adam.adam_update(self.step_count, hp["lr"], hp["betas"][0], hp["betas"][1], hp["eps"],
+                                      hp["weight_decay"], True, tp, np.ascontiguousarray(tg), tm, tv, loss_scale)
+                continue
+            c, s, e, g = call
             hp = self.groups[g]
             grad = self._prepared_grad(h16[c][s:e].view(np.float16))
             p = np.ascontiguousarray(p32[c][s:e])

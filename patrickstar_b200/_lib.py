@@ -40,8 +40,11 @@ CHUNK_DESC_DTYPE = np.dtype(
     [("p32", "<u8"), ("exp_avg", "<u8"), ("exp_avg_sq", "<u8"), ("h16", "<u8"),
      ("numel", "<u4"), ("seg_begin", "<u4"), ("seg_end", "<u4"), ("reserved", "<u4")])
 SEGMENT_DTYPE = np.dtype([("start", "<u4"), ("end", "<u4"), ("slot", "<u4"), ("reserved", "<u4")])
+TENSOR_DESC_DTYPE = np.dtype([("p32", "<u8"), ("grad", "<u8"), ("exp_avg", "<u8"), ("exp_avg_sq", "<u8"),
+                              ("numel", "<u8"), ("slot", "<u4"), ("reserved", "<u4")])
 OFFLOAD_CHUNK_DTYPE = np.dtype([("p32_host", "<u8"), ("exp_avg_host", "<u8"), ("exp_avg_sq_host", "<u8"),
                                 ("numel", "<u4"), ("desc_index", "<u4")])
+assert TENSOR_DESC_DTYPE.itemsize == 48
 assert CHUNK_DESC_DTYPE.itemsize == 48 and SEGMENT_DTYPE.itemsize == 16 and OFFLOAD_CHUNK_DTYPE.itemsize == 32
 
 
@@ -68,7 +71,8 @@ class HyperSlot(C.Structure):
                 ("beta1_minus1", C.c_float), ("beta2_minus1", C.c_float), ("bias2_sqrt", C.c_float),
                 ("eps", C.c_float), ("step_size", C.c_float), ("weight_decay", C.c_float),
                 ("w_decay", C.c_float), ("clip", C.c_float), ("grad_divisor", C.c_float),
-                ("adamw_mode", C.c_int32), ("inv_loss_scale", C.c_float), ("reserved", C.c_int32 * 2)]
+                ("adamw_mode", C.c_int32), ("inv_loss_scale", C.c_float), ("inv_grad_divisor", C.c_float),
+                ("reserved", C.c_int32)]
 
 
 class StepCtrl(C.Structure):
@@ -114,6 +118,11 @@ SIGNATURES = {
     "ps_offload_last_cuda_error": (C.c_int, []),
     "ps_chunk_step_fused": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, _p, C.c_int, _p]),
     "ps_chunk_step_p2p": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, C.c_int, _p]),
+    "ps_fused_pipe_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "ps_fused_pipe_destroy": (C.c_int, [_p]),
+    "ps_chunk_step_fused_staged": (C.c_int, [_p, _p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, _p, C.c_int, _p, _p]),
+    "ps_restore_fp16": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p]),
+    "ps_tensor_table_step": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p]),
     "ps_p2p_reduce_probe": (C.c_int, [_p, _p, _p, C.c_int, _p, C.c_size_t, _p]),
     "ps_multimem_reduce_probe": (C.c_int, [_p, _p, C.c_size_t, _p]),
     "ps_scaler_read": (C.c_int, [_p, C.POINTER(ScalerState), _p]),

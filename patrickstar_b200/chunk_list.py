@@ -59,6 +59,7 @@ class Piece:
     start: int
     end: int
     group: int
+    tensor_index: int = -1   # position of the piece's tensor in registration order
 
 
 class ChunkLayout:
@@ -199,11 +200,11 @@ class ChunkLayout:
             return self._piece_cache
         out = []
         cs = self.chunk_size
-        for t in self.tensors:
+        for ti, t in enumerate(self.tensors):
             c, off, rest = t.chunk_id, t.start_offset, t.numel
             while rest > 0:
                 take = min(rest, cs - off)
-                out.append(Piece(c, off, off + take, t.group))
+                out.append(Piece(c, off, off + take, t.group, ti))
                 rest -= take
                 c += 1
                 off = 0

@@ -65,6 +65,10 @@ class ChunkClient:
         self.n_resident = 0
         self.local_ids = []
         self._pending = []    # (name, nn.Parameter) registered from a module, placed at allocate()
+        # parameters managed by torch instead of the chunk list (the reference's TORCH_BASED
+        # kind, patrickstar/core/preprocess.py:351-369): name -> (fp32 nn.Parameter, number of
+        # chunk tensors registered before it, i.e. its place in the optimizer's visiting order)
+        self.torch_params = {}
 
     # ------------------------------------------------------------- registration
     def append_tensor_list(self, specs, shapes=None):
@@ -73,15 +77,37 @@ class ChunkClient:
     def append_tensor(self, name, numel, group=0, shape=None):
         return self.layout.append_tensor(name, numel, group, shape)
 
-    def register_module(self, module, group_of=None):
+    def append_torch_param(self, name, param):
+        """Register a parameter that stays outside the chunk list: fp32, updated in
+        place from its fp32 ``.grad``, no fp16 slot (the reference keeps the
+        CPU-embedding weights this way, patrickstar/core/preprocess.py:351-369,
+        patrickstar/ops/fp16_cpu_adam.py:345-353).  Its place in the optimizer's
+        visiting order is after the chunk tensors registered so far."""
+        if name in self.torch_params or name in self.layout._by_name:
+            raise ValueError("duplicate tensor name %r" % name)
+        if self.layout._frozen:
+            raise RuntimeError("layout is frozen")
+        self.torch_params[name] = (param, len(self.layout.tensors))
+        return param
+
+    def register_module(self, module, group_of=None, torch_based=None):
         """Register every parameter of an nn.Module, one atomic list per
         sub-module as the reference's pre-process context does
         (patrickstar/core/preprocess.py:341-435).  ``group_of(name, param)``
-        gives the hyper-parameter group index (default 0)."""
+        gives the hyper-parameter group index (default 0); parameters for which
+        ``torch_based(name, param)`` is true stay outside the chunk list as fp32
+        torch parameters (``append_torch_param``)."""
         for mod_name, mod in module.named_modules():
             specs, shapes, plist = [], [], []
             for pname, p in mod.named_parameters(recurse=False):
                 full = (mod_name + "." if mod_name else "") + pname
+                if torch_based is not None and torch_based(full, p):
+                    if specs:   # keep the visiting order: flush the chunk tensors seen so far
+                        self.layout.append_tensor_list(specs, shapes)
+                        self._pending.extend(plist)
+                        specs, shapes, plist = [], [], []
+                    self.append_torch_param(full, p)
+                    continue
                 g = group_of(full, p) if group_of else 0
                 specs.append((full, p.numel(), g))
                 shapes.append(tuple(p.shape))
@@ -100,19 +126,9 @@ class ChunkClient:
         cs = lay.chunk_size
         self.local_ids = lay.local_chunk_ids(self.rank)
         n_local = len(self.local_ids)
-        per_chunk = 3 * 4 * cs
-        if state_budget_bytes is None:
-            self.n_resident = n_local
-        elif state_budget_bytes == "auto":
-            # what the reference derives from its memory tracer: the chunks that fit
-            # into the GPU memory left over, scaled by margin_use_ratio
-            # (patrickstar/core/memtracer/memtracer.py:190-227, default ratio 0.8)
-            ratio = (self.config.get("mem_tracer", {}) or {}).get("margin_use_ratio", 0.8)
-            free, _ = torch.cuda.mem_get_info(self.device)
-            free -= 2 * lay.n_chunks * cs  # the fp16 chunk list allocated below
-            self.n_resident = max(0, min(n_local, int(free * ratio) // per_chunk))
-        else:
-            self.n_resident = max(0, min(n_local, int(state_budget_bytes) // per_chunk))
+        self._budget = state_budget_bytes
+        # the fp16 chunk list is allocated below: it comes out of what is free now
+        self.n_resident = self._derive_n_resident(state_budget_bytes, reserve=2 * lay.n_chunks * cs)
         n_off = n_local - self.n_resident
         dev = self.device
         if self.symmetric and self.world_size > 1:
@@ -153,7 +169,74 @@ class ChunkClient:
             for k, c in enumerate(self.local_ids):
                 self.chunk_state(k)[0].copy_(self.fp16_chunk(c).float())
         self._pending = []
+        for name, (p, _) in self.torch_params.items():
+            p.data = p.data.to(device=dev, dtype=torch.float32)
         return self
+
+    def _derive_n_resident(self, budget, reserve=0, held=0):
+        """How many local chunks keep their fp32 state in HBM.  ``None``: all;
+        a number: that many bytes; ``"auto"``: what the reference derives from its
+        memory tracer every step — the chunks that fit into the GPU memory left
+        over, scaled by margin_use_ratio
+        (patrickstar/core/memtracer/memtracer.py:190-227, default ratio 0.8).
+        ``reserve`` bytes are about to be allocated by the caller, ``held`` bytes of
+        state are already in HBM and count as available."""
+        n_local = len(self.local_ids)
+        per_chunk = 3 * 4 * self.layout.chunk_size
+        if budget is None:
+            return n_local
+        if budget == "auto":
+            ratio = (self.config.get("mem_tracer", {}) or {}).get("margin_use_ratio", 0.8)
+            free, _ = self.mem_get_info(self.device)
+            return max(0, min(n_local, int((free - reserve + held) * ratio) // per_chunk))
+        return max(0, min(n_local, int(budget) // per_chunk))
+
+    # replaced by tests to play a device that is short of memory
+    mem_get_info = staticmethod(torch.cuda.mem_get_info)
+
+    def rebalance(self, state_budget_bytes=None):
+        """Re-derive the hybrid placement from the memory that is free NOW and move
+        chunk states between HBM and pinned host memory accordingly — what the
+        reference does before every step (``margin_chunk_num_for_gpu_adam``,
+        patrickstar/ops/fp16_cpu_adam.py:523-528; the chunk moves themselves happen
+        in patrickstar/core/chunk_data.py:275-366).  ``state_budget_bytes``
+        defaults to what ``allocate`` was given.  Returns True when the split
+        changed; the optimizer then has to rebuild its tables
+        (``FP16Adam.rebalance`` does both)."""
+        budget = self._budget if state_budget_bytes is None else state_budget_bytes
+        if budget is None:
+            return False
+        cs = self.layout.chunk_size
+        n_local = len(self.local_ids)
+        old = self.n_resident
+        new = self._derive_n_resident(budget, held=3 * 4 * cs * old)
+        self._budget = budget
+        if new == old:
+            return False
+        dev = self.device
+        torch.cuda.current_stream(dev).synchronize()   # no step may be in flight on the states
+        names = ("p32", "exp_avg", "exp_avg_sq")
+        for name in names:   # one kind at a time: the transient extra HBM is one third of the state
+            d_old, h_old = getattr(self, name), getattr(self, name + "_host")
+            d_new = torch.empty(new * cs, dtype=torch.float32, device=dev)
+            n_off = n_local - new
+            h_new = torch.empty(n_off * cs, dtype=torch.float32).pin_memory() if n_off else None
+            keep = min(old, new)
+            d_new[:keep * cs].copy_(d_old[:keep * cs])
+            if new > old:    # chunks old..new-1 come up from the host
+                d_new[old * cs:new * cs].copy_(h_old[:(new - old) * cs])
+                if n_off:
+                    h_new.copy_(h_old[(new - old) * cs:])
+            else:            # chunks new..old-1 go down to the host
+                h_new[:(old - new) * cs].copy_(d_old[new * cs:old * cs])
+                if h_old is not None:
+                    h_new[(old - new) * cs:].copy_(h_old)
+            torch.cuda.current_stream(dev).synchronize()
+            setattr(self, name, d_new)
+            setattr(self, name + "_host", h_new)
+            del d_old, h_old
+        self.n_resident = new
+        return True
 
     # -------------------------------------------------------------------- views
     def fp16_chunk(self, chunk_id):

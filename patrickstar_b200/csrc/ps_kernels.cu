@@ -22,6 +22,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <new>
 #include <unordered_map>
 
 namespace {
@@ -40,6 +41,12 @@ struct Tuning {
     int blocks_per_sm = 0; // 0 = as many as the occupancy calculator allows
     int scan_unroll = 4;
     int bulk = 0;          // 2..4: chunk step with bulk-async (TMA 1-D) staging, that many stages deep
+    int fused_depth = 4;   // reduced-gradient loads in flight per thread of the fused multi-GPU step
+    int fused_blocks_per_sm = 0;
+    int pull_blocks_per_sm = 2;    // staged form of the fused step: grid of the gradient puller
+    int staged_blocks_per_sm = 1;  // ... and of the step kernel that runs beside it
+    int p2p_unroll = 0;    // 0 = chosen from the world size
+    int p2p_blocks_per_sm = 0;
 };
 Tuning g_tune;
 
@@ -95,6 +102,7 @@ struct Slot {
         divisor;
     int adamw;
     float inv_scale;  // 1 / loss_scale when that is exact (power-of-two scale), else 0
+    float inv_div;    // float(1 / divisor): the factor torch multiplies with for `payload /= world`
 };
 
 __device__ __forceinline__ Slot load_slot(const ps_hyper_slot* s)
@@ -118,6 +126,7 @@ __device__ __forceinline__ Slot load_slot(const ps_hyper_slot* s)
     r.divisor = __uint_as_float(c.w);
     r.adamw = (int)d.x;
     r.inv_scale = __uint_as_float(d.y);
+    r.inv_div = __uint_as_float(d.z);
     return r;
 }
 
@@ -138,6 +147,7 @@ __device__ __forceinline__ Slot slot_from_value(const ps_hyper_slot& s)
     r.divisor = s.grad_divisor;
     r.adamw = s.adamw_mode;
     r.inv_scale = s.inv_loss_scale;
+    r.inv_div = s.inv_grad_divisor;
     return r;
 }
 
@@ -150,14 +160,27 @@ __device__ __forceinline__ uint32_t float_to_half_bits(float f)
     return (uint32_t)__half_as_ushort(__float2half_rn(f));
 }
 
+// clamp_(-c, c) as torch does it: a NaN stays a NaN (fminf / fmaxf alone would
+// turn it into -c and hide a diverged gradient when no overflow gate is active).
+__device__ __forceinline__ float clamp_keep_nan(float g, float c)
+{
+    return g != g ? g : fminf(fmaxf(g, -c), c);
+}
+
 // fp16 gradient as the step sees it: the fp16 `payload /= world_size` of
 // patrickstar/core/client.py:838 and the fp16 clamp_ of
 // patrickstar/ops/fp16_cpu_adam.py:365-379, each rounded back to fp16.
+// The division of a CUDA fp16 tensor by a Python scalar is computed by torch as
+// half(float(g) * (1.0f / world)); for a power-of-two world that equals the true
+// quotient, for any other it can differ from it by one fp16 ulp.
 __device__ __forceinline__ float grad_from_half(uint32_t h, const Slot& s)
 {
     float g = half_bits_to_float(h);
-    if (s.divisor > 1.f) g = half_bits_to_float(float_to_half_bits(__fdiv_rn(g, s.divisor)));
-    if (s.clip > 0.f) g = half_bits_to_float(float_to_half_bits(fminf(fmaxf(g, -s.clip), s.clip)));
+    if (s.divisor > 1.f) {
+        const float inv = s.inv_div != 0.f ? s.inv_div : __fdiv_rn(1.0f, s.divisor);
+        g = half_bits_to_float(float_to_half_bits(__fmul_rn(g, inv)));
+    }
+    if (s.clip > 0.f) g = half_bits_to_float(float_to_half_bits(clamp_keep_nan(g, s.clip)));
     return g;
 }
 
@@ -679,7 +702,15 @@ chunk_step_bulk_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chun
         const uint32_t s = cons_n % kBulkStages;
         const bool arrived = mbar_wait(&full_bar[s], (cons_n / kBulkStages) & 1u);
         if (!__syncthreads_and(arrived)) {
-            if (threadIdx.x == 0) atomicOr(const_cast<int32_t*>(&ctrl->error), 2);
+            // Gave up on this stage.  Copies of the stages issued after it may still be
+            // landing in this CTA's shared memory, which the next resident CTA may own:
+            // wait (bounded again) for each of them before leaving.
+            if (threadIdx.x == 0) {
+                atomicOr(const_cast<int32_t*>(&ctrl->error), 2);
+                for (uint32_t i = cons_n; i < prod_n; ++i)
+                    mbar_wait(&full_bar[i % kBulkStages], (i / kBulkStages) & 1u);
+            }
+            __syncthreads();
             return;
         }
         // thread i owns elements [4i, 4i+4) and [1024+4i, 1024+4i+4) of the tile:
@@ -719,8 +750,6 @@ chunk_step_bulk_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chun
 // ahead of the rest: a thread keeps that many 16-byte multimem loads in flight
 // in a register ring while it works on the current tile (one 8-element group
 // per thread and tile, to leave the registers to the ring).
-constexpr int kFusedDepth = 4;
-
 __device__ __forceinline__ uint4 fused_prefetch(const ps_chunk_desc* chunks, uint32_t tiles_per_chunk,
                                                 uint64_t t, uint64_t total, int skip, const McCtx& mc)
 {
@@ -736,6 +765,7 @@ __device__ __forceinline__ uint4 fused_prefetch(const ps_chunk_desc* chunks, uin
     return g;
 }
 
+template <int kFusedDepth>
 __global__ void __launch_bounds__(kThreads)
 chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
                         uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
@@ -801,6 +831,137 @@ chunk_step_p2p_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunk
             step_tile<U, false, true, kColl>(d, segs, slots, tile_base, mc);
     }
     __threadfence_system();
+}
+
+// Restore alone (fp16_cpu_adam.py:298-309): fp16 slot := half(fp32 master) for every
+// segment of every chunk, no control block.
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+chunk_restore_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
+                     uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    const uint64_t total = (uint64_t)n_chunks * tiles_per_chunk;
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t c = (uint32_t)(t / tiles_per_chunk);
+        const uint32_t lt = (uint32_t)(t - (uint64_t)c * tiles_per_chunk);
+        const ps_chunk_desc d = load_desc(chunks + c);
+        const uint32_t tile_base = d.reserved + lt * kTile;
+        if (tile_base < d.numel) step_tile<U, true, true>(d, segs, nullptr, tile_base);
+    }
+}
+
+// Staged form of the fused multi-GPU step, stage 1: the switch-side sum of one
+// owned chunk's gradients is pulled into a local staging buffer.  Nothing but
+// loads and stores, so a thread keeps kPullDepth 16-byte reduced loads in flight
+// and the grid can stay small beside the step kernel.  Ragged ends (the last
+// numel % 8 elements) are left to the step kernel's element-wise path, which
+// reads them through the multicast mapping itself.
+constexpr int kPullDepth = 8;
+__global__ void __launch_bounds__(kThreads)
+fused_pull_kernel(const ps_chunk_desc* __restrict__ chunk, const ps_step_ctrl* __restrict__ ctrl,
+                  uint16_t* __restrict__ staging, long long mc_delta)
+{
+    if (__ldg(&ctrl->skip)) return;  // a skipped step restores from the master: no gradients needed
+    const ps_chunk_desc d = load_desc(chunk);
+    const uint32_t n_vec = d.numel / kVec;
+    const char* src = reinterpret_cast<const char*>(d.h16) + mc_delta;
+    const uint32_t stride = gridDim.x * kThreads;
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n_vec; i += stride * kPullDepth) {
+        uint4 q[kPullDepth];
+#pragma unroll
+        for (int k = 0; k < kPullDepth; ++k) {
+            const uint32_t j = i + (uint32_t)k * stride;
+            if (j < n_vec) q[k] = mm_ld_reduce_f16x8(src + (size_t)j * 16);
+        }
+#pragma unroll
+        for (int k = 0; k < kPullDepth; ++k) {
+            const uint32_t j = i + (uint32_t)k * stride;
+            if (j < n_vec) reinterpret_cast<uint4*>(staging)[j] = q[k];
+        }
+    }
+}
+
+// Stage 2: the chunk step with the reduced gradients taken from the staging
+// buffer and the fp16 params stored to every rank through the multicast mapping.
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+chunk_step_staged_kernel(const ps_chunk_desc* __restrict__ chunk, uint32_t tiles_per_chunk,
+                         const ps_segment* __restrict__ segs, const ps_step_ctrl* __restrict__ ctrl,
+                         const uint16_t* __restrict__ staging, McCtx mc)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    const int skip = __ldg(&ctrl->skip);
+    const ps_hyper_slot* slots = ctrl->slots;
+    const ps_chunk_desc d = load_desc(chunk);
+    for (uint32_t lt = blockIdx.x; lt < tiles_per_chunk; lt += gridDim.x) {
+        const uint32_t tile_base = lt * kTile;
+        if (tile_base >= d.numel) continue;
+        if (skip) {
+            step_tile<U, true, true, 1, false>(d, segs, slots, tile_base, mc);
+        } else {
+            uint4 g[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const uint32_t e = tile_base + (uint32_t)(j * kThreads + threadIdx.x) * kVec;
+                g[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (e + kVec <= d.numel) g[j] = ld_stream(reinterpret_cast<const uint4*>(staging + e));
+            }
+            step_tile<U, false, true, 1, true>(d, segs, slots, tile_base, mc, g);
+        }
+    }
+    __threadfence_system();
+}
+
+// Parameters managed by torch (fp32 parameter = master, fp32 gradient, no fp16
+// slot; fp16_cpu_adam.py:345-353): the whole table in one launch.  Tiles of
+// kThreads * 4 elements are numbered tensor-major.  The gradient is unscaled and
+// (when clipping is on) clamped in fp32, as the reference's clamp_ on the fp32
+// grad tensor does; it is not divided by the world size.
+__global__ void __launch_bounds__(kThreads)
+tensor_table_step_kernel(const ps_tensor_desc* __restrict__ tensors, uint32_t n_tensors,
+                         uint32_t tiles_per_tensor, const ps_step_ctrl* __restrict__ ctrl)
+{
+    if (__ldg(&ctrl->skip)) return;
+    constexpr uint32_t kTile = kThreads * 4;
+    const uint64_t total = (uint64_t)n_tensors * tiles_per_tensor;
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t c = (uint32_t)(t / tiles_per_tensor);
+        const uint64_t lt = t - (uint64_t)c * tiles_per_tensor;
+        const ps_tensor_desc d = tensors[c];
+        const uint64_t e = lt * kTile + (uint64_t)threadIdx.x * 4;
+        if (e >= d.numel) continue;
+        const Slot s = load_slot(ctrl->slots + d.slot);
+        const bool vec = ((reinterpret_cast<uintptr_t>(d.p32) | reinterpret_cast<uintptr_t>(d.grad) |
+                           reinterpret_cast<uintptr_t>(d.exp_avg) |
+                           reinterpret_cast<uintptr_t>(d.exp_avg_sq)) & 15u) == 0 && e + 4 <= d.numel;
+        if (vec) {
+            const float4 gq = ld_stream(reinterpret_cast<const float4*>(d.grad + e));
+            const float4 pq = ld_stream(reinterpret_cast<const float4*>(d.p32 + e));
+            const float4 mq = ld_stream(reinterpret_cast<const float4*>(d.exp_avg + e));
+            const float4 vq = ld_stream(reinterpret_cast<const float4*>(d.exp_avg_sq + e));
+            float g[4] = {gq.x, gq.y, gq.z, gq.w}, pp[4] = {pq.x, pq.y, pq.z, pq.w};
+            float m[4] = {mq.x, mq.y, mq.z, mq.w}, v[4] = {vq.x, vq.y, vq.z, vq.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (s.clip > 0.f) g[k] = clamp_keep_nan(g[k], s.clip);
+                adam_element(g[k], pp[k], m[k], v[k], s);
+            }
+            st_stream(reinterpret_cast<float4*>(d.p32 + e), make_float4(pp[0], pp[1], pp[2], pp[3]));
+            st_stream(reinterpret_cast<float4*>(d.exp_avg + e), make_float4(m[0], m[1], m[2], m[3]));
+            st_stream(reinterpret_cast<float4*>(d.exp_avg_sq + e), make_float4(v[0], v[1], v[2], v[3]));
+        } else {
+            const uint64_t e_end = e + 4 < d.numel ? e + 4 : d.numel;
+            for (uint64_t i = e; i < e_end; ++i) {
+                float g = d.grad[i], pp = d.p32[i], m = d.exp_avg[i], v = d.exp_avg_sq[i];
+                if (s.clip > 0.f) g = clamp_keep_nan(g, s.clip);
+                adam_element(g, pp, m, v, s);
+                d.p32[i] = pp;
+                d.exp_avg[i] = m;
+                d.exp_avg_sq[i] = v;
+            }
+        }
+    }
 }
 
 // dst[i] = the peer-to-peer kernel's reduced gradient of the element at byte
@@ -1032,7 +1193,8 @@ __device__ void derive_slot(ps_hyper_slot* out, const ps_group_hyper& g, float b
     out->grad_divisor = divisor;
     out->adamw_mode = g.adamw_mode;
     out->inv_loss_scale = loss_scale > 0.f ? exact_reciprocal_or_zero(loss_scale) : 0.f;
-    out->reserved[0] = out->reserved[1] = 0;
+    out->inv_grad_divisor = divisor > 1.f ? __fdiv_rn(1.0f, divisor) : 0.f;
+    out->reserved = 0;
 }
 
 __device__ void pow_lookup(const float* tab, uint64_t tab_len, int group, uint64_t t, float beta1,
@@ -1195,6 +1357,7 @@ struct AdamClock {
     size_t step = 0;
     float bias_correction1 = 1.0f, bias_correction2 = 1.0f;
     bool adamw_mode = true;
+    std::mutex mu;  // held across increment_step / update_state / slot of one adam_update call
 
     void increment_step(size_t s, float beta1, float beta2)
     {
@@ -1315,6 +1478,7 @@ int launch_chunk_step_bulk(const ps_chunk_desc* chunks, uint32_t n_chunks, uint3
     return after_launch();
 }
 
+template <int kDepth>
 int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
                             const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
 {
@@ -1322,9 +1486,12 @@ int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint
     uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
     uint64_t total = (uint64_t)tpc * n_chunks;
     int grid = 1;
-    int rc = grid_for(chunk_step_fused_kernel, total, &grid, 1);
+    const int saved = g_tune.blocks_per_sm;
+    g_tune.blocks_per_sm = g_tune.fused_blocks_per_sm;
+    int rc = grid_for(chunk_step_fused_kernel<kDepth>, total, &grid, 1);
+    g_tune.blocks_per_sm = saved;
     if (rc != PS_OK) return rc;
-    chunk_step_fused_kernel<<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    chunk_step_fused_kernel<kDepth><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
     return after_launch();
 }
 
@@ -1335,11 +1502,34 @@ int launch_chunk_step_p2p(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32
     constexpr uint32_t kTile = kThreads * kVec * U;
     uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
     int grid = 1;
+    const int saved = g_tune.blocks_per_sm;
+    g_tune.blocks_per_sm = g_tune.p2p_blocks_per_sm;
     int rc = grid_for(chunk_step_p2p_kernel<U, kColl>, (uint64_t)tpc * n_chunks, &grid, 2);
+    g_tune.blocks_per_sm = saved;
     if (rc != PS_OK) return rc;
     chunk_step_p2p_kernel<U, kColl><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
     return after_launch();
 }
+
+template <int U>
+int launch_chunk_restore(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
+                         const ps_segment* segs, cudaStream_t st)
+{
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    int grid = 1;
+    int rc = grid_for(chunk_restore_kernel<U>, (uint64_t)tpc * n_chunks, &grid, 2);
+    if (rc != PS_OK) return rc;
+    chunk_restore_kernel<U><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs);
+    return after_launch();
+}
+
+// Stream and events of ps_chunk_step_fused_staged (two staging slots).
+struct FusedPipe {
+    int device = -1;
+    cudaStream_t pull = nullptr;
+    cudaEvent_t start = nullptr, full[2] = {nullptr, nullptr}, freed[2] = {nullptr, nullptr};
+};
 
 template <int U, bool kWrite16>
 int launch_tensor_step(const ps_chunk_desc& d, uint32_t head, const ps_hyper_slot& slot,
@@ -1454,6 +1644,24 @@ int ps_tune(const char* key, int value)
     } else if (!strcmp(key, "bulk")) {
         if (value != 0 && (value < 2 || value > 4)) return PS_ERR_INVALID;
         g_tune.bulk = value;
+    } else if (!strcmp(key, "fused_depth")) {
+        if (value != 2 && value != 4 && value != 8) return PS_ERR_INVALID;
+        g_tune.fused_depth = value;
+    } else if (!strcmp(key, "fused_blocks_per_sm")) {
+        if (value < 0 || value > 32) return PS_ERR_INVALID;
+        g_tune.fused_blocks_per_sm = value;
+    } else if (!strcmp(key, "pull_blocks_per_sm")) {
+        if (value < 0 || value > 32) return PS_ERR_INVALID;
+        g_tune.pull_blocks_per_sm = value;
+    } else if (!strcmp(key, "staged_blocks_per_sm")) {
+        if (value < 0 || value > 32) return PS_ERR_INVALID;
+        g_tune.staged_blocks_per_sm = value;
+    } else if (!strcmp(key, "p2p_blocks_per_sm")) {
+        if (value < 0 || value > 32) return PS_ERR_INVALID;
+        g_tune.p2p_blocks_per_sm = value;
+    } else if (!strcmp(key, "p2p_unroll")) {
+        if (value != 0 && value != 1 && value != 2) return PS_ERR_INVALID;
+        g_tune.p2p_unroll = value;
     } else if (!strcmp(key, "scan_unroll")) {
         if (value != 1 && value != 2 && value != 4) return PS_ERR_INVALID;
         g_tune.scan_unroll = value;
@@ -1498,6 +1706,7 @@ int ps_adam_get_state(int optimizer_id, float out[4], uint64_t* step)
     std::lock_guard<std::mutex> lk(g_opt_mu);
     auto it = g_optimizers.find(optimizer_id);
     if (it == g_optimizers.end()) return PS_ERR_UNKNOWN_ID;
+    std::lock_guard<std::mutex> lk2(it->second->mu);
     out[0] = it->second->betta1_t;
     out[1] = it->second->betta2_t;
     out[2] = it->second->bias_correction1;
@@ -1530,10 +1739,15 @@ int ps_adam_update(int optimizer_id, size_t step, float lr, float beta1, float b
     if (oa & 1u) return PS_ERR_ALIGN;
     // the history-dependent state advances even for an empty tensor, as in the
     // reference (ds_adam_step calls IncrementStep before looking at the size)
-    clock->increment_step(step, beta1, beta2);
-    clock->update_state(lr, epsilon, weight_decay, bias_correction == 1);
+    ps_hyper_slot slot;
+    {
+        // two threads sharing one optimizer id must not interleave inside the beta^t history
+        std::lock_guard<std::mutex> lk(clock->mu);
+        clock->increment_step(step, beta1, beta2);
+        clock->update_state(lr, epsilon, weight_decay, bias_correction == 1);
+        slot = clock->slot(loss_scale);
+    }
     if (n == 0) return PS_OK;
-    const ps_hyper_slot slot = clock->slot(loss_scale);
     cudaStream_t st = (cudaStream_t)stream;
 
     // Vector path: fp16 grads, fp16 output (if any) in the gradient's own
@@ -1589,6 +1803,9 @@ int ps_table_check(const ps_chunk_desc* chunks, uint32_t n_chunks, const ps_segm
             !aligned16(d.h16))
             return PS_ERR_ALIGN;
         if (d.numel > chunk_capacity) return PS_ERR_TABLE;
+        // `reserved` is the first element the kernel touches: the 128-bit accesses start there
+        if (d.reserved % 2048u != 0u) return PS_ERR_TABLE;
+        if (d.reserved != 0u && d.reserved >= d.numel) return PS_ERR_TABLE;
         if (d.seg_begin > d.seg_end || d.seg_end > n_segs) return PS_ERR_TABLE;
         if (d.seg_begin == d.seg_end && d.numel != 0) return PS_ERR_TABLE;
         uint32_t prev_end = 0;
@@ -1747,8 +1964,147 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
-    return launch_chunk_step_fused(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc,
-                                   (cudaStream_t)stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (g_tune.fused_depth) {
+        case 2: return launch_chunk_step_fused<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 8: return launch_chunk_step_fused<8>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        default: return launch_chunk_step_fused<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    }
+}
+
+int ps_fused_pipe_create(void** pipe_out)
+{
+    if (pipe_out == nullptr) return PS_ERR_INVALID;
+    auto* p = new FusedPipe();
+    int rc = PS_OK;
+    do {
+        if (cudaGetDevice(&p->device) != cudaSuccess) { rc = PS_ERR_CUDA; break; }
+        if (cudaStreamCreateWithFlags(&p->pull, cudaStreamNonBlocking) != cudaSuccess) { rc = PS_ERR_CUDA; break; }
+        cudaEvent_t* evs[5] = {&p->start, &p->full[0], &p->full[1], &p->freed[0], &p->freed[1]};
+        for (auto* e : evs)
+            if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess) { rc = PS_ERR_CUDA; break; }
+    } while (0);
+    if (rc != PS_OK) {
+        g_last_cuda_error = (int)cudaGetLastError();
+        ps_fused_pipe_destroy(p);
+        return rc;
+    }
+    *pipe_out = p;
+    return PS_OK;
+}
+
+int ps_fused_pipe_destroy(void* pipe)
+{
+    if (pipe == nullptr) return PS_ERR_INVALID;
+    auto* p = static_cast<FusedPipe*>(pipe);
+    cudaEvent_t evs[5] = {p->start, p->full[0], p->full[1], p->freed[0], p->freed[1]};
+    for (auto e : evs)
+        if (e) cudaEventDestroy(e);
+    if (p->pull) cudaStreamDestroy(p->pull);
+    delete p;
+    return PS_OK;
+}
+
+int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint32_t n_chunks,
+                               uint32_t max_numel, const ps_segment* segs_dev, const ps_step_ctrl* ctrl_dev,
+                               const void* fp16_local_base, const void* fp16_multicast_base,
+                               const uint64_t* peer_bases_dev, int world_size, uint16_t* staging_dev,
+                               void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (pipe == nullptr || chunks_dev == nullptr || segs_dev == nullptr || ctrl_dev == nullptr ||
+        fp16_local_base == nullptr || fp16_multicast_base == nullptr || peer_bases_dev == nullptr ||
+        staging_dev == nullptr)
+        return PS_ERR_INVALID;
+    if (world_size < 2 || world_size > 64) return PS_ERR_INVALID;
+    if (((uintptr_t)fp16_local_base | (uintptr_t)fp16_multicast_base | (uintptr_t)staging_dev) & 15u)
+        return PS_ERR_ALIGN;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    auto* p = static_cast<FusedPipe*>(pipe);
+    cudaStream_t st = (cudaStream_t)stream;
+    McCtx mc;
+    mc.mc_delta = (long long)((intptr_t)fp16_multicast_base - (intptr_t)fp16_local_base);
+    mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
+    mc.world = world_size;
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    constexpr int U = 1;  // HBM is lightly loaded beside the links: leave the registers to the puller
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    const uint32_t tpc = (uint32_t)(((uint64_t)max_numel + kTile - 1) / kTile);
+    const int pull_grid = di.sm_count * (g_tune.pull_blocks_per_sm > 0 ? g_tune.pull_blocks_per_sm : 2);
+    uint64_t step_grid = (uint64_t)di.sm_count * (g_tune.staged_blocks_per_sm > 0 ? g_tune.staged_blocks_per_sm : 1);
+    if (step_grid > tpc) step_grid = tpc;
+    // staging slot of chunk k: k % 2, each slot max_numel rounded up to a whole 16-byte group
+    const size_t slot_elems = ((size_t)max_numel + kVec - 1) / kVec * kVec;
+    PS_CUDA(cudaEventRecord(p->start, st));
+    PS_CUDA(cudaStreamWaitEvent(p->pull, p->start, 0));
+    for (uint32_t k = 0; k < n_chunks; ++k) {
+        const int s = (int)(k & 1u);
+        uint16_t* slot = staging_dev + (size_t)s * slot_elems;
+        if (k >= 2) PS_CUDA(cudaStreamWaitEvent(p->pull, p->freed[s], 0));
+        fused_pull_kernel<<<pull_grid, kThreads, 0, p->pull>>>(chunks_dev + k, ctrl_dev, slot, mc.mc_delta);
+        rc = after_launch();
+        if (rc != PS_OK) return rc;
+        PS_CUDA(cudaEventRecord(p->full[s], p->pull));
+        PS_CUDA(cudaStreamWaitEvent(st, p->full[s], 0));
+        chunk_step_staged_kernel<U><<<(int)step_grid, kThreads, 0, st>>>(chunks_dev + k, tpc, segs_dev,
+                                                                       ctrl_dev, slot, mc);
+        rc = after_launch();
+        if (rc != PS_OK) return rc;
+        PS_CUDA(cudaEventRecord(p->freed[s], st));
+    }
+    return PS_OK;
+}
+
+int ps_restore_fp16(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
+                    const ps_segment* segs_dev, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (chunks_dev == nullptr || segs_dev == nullptr) return PS_ERR_INVALID;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    return launch_chunk_restore<2>(chunks_dev, n_chunks, max_numel, segs_dev, (cudaStream_t)stream);
+}
+
+int ps_tensor_table_step(const ps_tensor_desc* tensors_host, uint32_t n_tensors, uint32_t n_slots,
+                         ps_tensor_desc* table_dev, const ps_step_ctrl* ctrl_dev, void* stream)
+{
+    if (n_tensors == 0) return PS_OK;
+    if (tensors_host == nullptr || table_dev == nullptr || ctrl_dev == nullptr) return PS_ERR_INVALID;
+    if (n_slots > PS_MAX_SLOTS) return PS_ERR_LIMIT;
+    if (n_tensors > PS_TENSOR_TABLE_MAX) return PS_ERR_LIMIT;
+    if (!aligned16(table_dev)) return PS_ERR_ALIGN;
+    uint64_t max_numel = 0;
+    for (uint32_t i = 0; i < n_tensors; ++i) {
+        const ps_tensor_desc& d = tensors_host[i];
+        if (d.numel == 0) continue;
+        if (!d.p32 || !d.grad || !d.exp_avg || !d.exp_avg_sq) return PS_ERR_INVALID;
+        if (((uintptr_t)d.p32 | (uintptr_t)d.grad | (uintptr_t)d.exp_avg | (uintptr_t)d.exp_avg_sq) & 3u)
+            return PS_ERR_ALIGN;
+        if (d.slot >= n_slots) return PS_ERR_TABLE;
+        if (d.numel >= (1ull << 40)) return PS_ERR_LIMIT;
+        if (d.numel > max_numel) max_numel = d.numel;
+    }
+    if (max_numel == 0) return PS_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    // The gradient pointers change from step to step (autograd allocates a new .grad), so the
+    // table travels with every call: through a pageable image owned by the library (one per
+    // calling thread), from which cudaMemcpyAsync has taken its bytes when it returns.
+    static thread_local std::unique_ptr<ps_tensor_desc[]> image;
+    if (!image) image.reset(new (std::nothrow) ps_tensor_desc[PS_TENSOR_TABLE_MAX]);
+    if (!image) return PS_ERR_INVALID;
+    memcpy(image.get(), tensors_host, (size_t)n_tensors * sizeof(ps_tensor_desc));
+    PS_CUDA(cudaMemcpyAsync(table_dev, image.get(), (size_t)n_tensors * sizeof(ps_tensor_desc),
+                            cudaMemcpyHostToDevice, st));
+    constexpr uint64_t kTile = kThreads * 4;
+    const uint64_t tpt = (max_numel + kTile - 1) / kTile;
+    if (tpt >= 0x7fffffffull) return PS_ERR_LIMIT;
+    int grid = 1;
+    int rc = grid_for(tensor_table_step_kernel, tpt * n_tensors, &grid, 2);
+    if (rc != PS_OK) return rc;
+    tensor_table_step_kernel<<<grid, kThreads, 0, st>>>(table_dev, n_tensors, (uint32_t)tpt, ctrl_dev);
+    return after_launch();
 }
 
 int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32_t max_numel,
@@ -1770,7 +2126,9 @@ int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32
     cudaStream_t st = (cudaStream_t)stream;
     // few ranks: few peer loads per group, so two groups per thread keep the link busy
     int rc;
-    if (world_size <= 2)
+    if (world_size <= 2 && g_tune.p2p_unroll == 1)
+        rc = launch_chunk_step_p2p<1, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 2)
         rc = launch_chunk_step_p2p<2, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
     else if (world_size <= 4)
         rc = launch_chunk_step_p2p<1, 24>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
@@ -1863,20 +2221,31 @@ int ps_chunk_step_static(const ps_chunk_desc* chunks_host, uint32_t n_chunks, ui
     if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
     int rc = ps_table_check(chunks_host, n_chunks, segs_host, n_segs, n_slots, max_numel);
     if (rc != PS_OK) return rc;
+    for (uint32_t c = 0; c < n_chunks; ++c)
+        if (chunks_host[c].reserved != 0u) return PS_ERR_TABLE;  // whole chunks only here
     unsigned char* base = nullptr;
     rc = static_scratch_address(&base);  // first call on a device: cudaGetSymbolAddress
     if (rc != PS_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    // the whole control block is rebuilt on the host and overwritten, so nothing
-    // of the previous call survives in it
-    ps_step_ctrl ctrl;
-    memset(&ctrl, 0, sizeof(ctrl));
-    ctrl.skip = skip ? 1 : 0;
-    for (uint32_t i = 0; i < n_slots; ++i) ctrl.slots[i] = slots_host[i];
-    PS_CUDA(cudaMemcpyAsync(base, &ctrl, sizeof(ctrl), cudaMemcpyHostToDevice, st));
-    PS_CUDA(cudaMemcpyAsync(base + kStaticChunkOff, chunks_host, (size_t)n_chunks * sizeof(ps_chunk_desc),
-                            cudaMemcpyHostToDevice, st));
-    PS_CUDA(cudaMemcpyAsync(base + kStaticSegOff, segs_host, (size_t)n_segs * sizeof(ps_segment),
+    // Host image of the device array, owned by the library, one per calling thread, in
+    // pageable memory: a cudaMemcpyAsync from pageable memory has taken its bytes by the
+    // time it returns, so neither this image nor the caller's tables (which may be pinned,
+    // where the copy would be truly asynchronous) are read after this call returns.
+    static thread_local std::unique_ptr<unsigned char[]> image;
+    if (!image) image.reset(new (std::nothrow) unsigned char[kStaticBytes]);
+    if (!image) return PS_ERR_INVALID;
+    // the whole control block is rebuilt and overwritten, so nothing of the previous call
+    // survives in it
+    ps_step_ctrl* ctrl = reinterpret_cast<ps_step_ctrl*>(image.get());
+    memset(ctrl, 0, kStaticCtrlBytes);
+    ctrl->skip = skip ? 1 : 0;
+    for (uint32_t i = 0; i < n_slots; ++i) ctrl->slots[i] = slots_host[i];
+    const size_t chunk_bytes = (size_t)n_chunks * sizeof(ps_chunk_desc);
+    const size_t seg_bytes = (size_t)n_segs * sizeof(ps_segment);
+    memcpy(image.get() + kStaticChunkOff, chunks_host, chunk_bytes);
+    memcpy(image.get() + kStaticSegOff, segs_host, seg_bytes);
+    PS_CUDA(cudaMemcpyAsync(base, image.get(), kStaticChunkOff + chunk_bytes, cudaMemcpyHostToDevice, st));
+    PS_CUDA(cudaMemcpyAsync(base + kStaticSegOff, image.get() + kStaticSegOff, seg_bytes,
                             cudaMemcpyHostToDevice, st));
     const ps_chunk_desc* chunks_dev = reinterpret_cast<const ps_chunk_desc*>(base + kStaticChunkOff);
     const ps_segment* segs_dev = reinterpret_cast<const ps_segment*>(base + kStaticSegOff);

@@ -15,6 +15,16 @@ Quirks kept on purpose (they decide the loss-scale trajectory):
     (engine.py:84-88); ``loss_scale == 0`` selects the dynamic scaler.
   * ``config=None`` crashes in the reference (``None.get``,
     runtime/__init__.py:74); here it means "all defaults".
+
+One key is added under the reference's ``client.opts`` block
+(runtime/__init__.py:60-71 holds ``with_mem_saving_comm`` etc. there):
+``fused_collectives`` — how a data-parallel step exchanges chunks.
+``"nccl"``: NCCL reduce-scatter / all-gather pipelined around the step kernel,
+each group's reduce-scatter fired from the backward hand-off;
+``"multimem"`` / ``"p2p"``: one kernel that does the reduction, the step and
+the gather over NVSwitch multicast memory or peer mappings; ``"auto"``
+(default): p2p for 2-3 ranks, multimem for more, nccl when symmetric memory
+cannot be set up.
 """
 import torch
 
@@ -33,7 +43,8 @@ def parse_config(config):
     """engine.py:53-105 as a pure function.  Returns a dict with optim_type,
     optim_params, scaler ("none" | ("static", scale) | ("dynamic", kwargs)),
     gradient_clipping, default_chunk_size."""
-    out = {"default_chunk_size": DEFAULT_CHUNK_SIZE, "gradient_clipping": -1, "scaler": "none"}
+    out = {"default_chunk_size": DEFAULT_CHUNK_SIZE, "gradient_clipping": -1, "scaler": "none",
+           "fused_collectives": "auto"}
     if config is None:
         out["optim_type"] = _DEFAULT_OPTIM["type"]
         out["optim_params"] = dict(_DEFAULT_OPTIM["params"])
@@ -64,7 +75,20 @@ def parse_config(config):
             out["scaler"] = ("static", ls["loss_scale"])
     if "gradient_clipping" in config:
         out["gradient_clipping"] = config["gradient_clipping"]
+    mode = ((config.get("client") or {}).get("opts") or {}).get("fused_collectives", "auto")
+    if mode not in ("auto", "nccl", "multimem", "p2p"):
+        raise ValueError("client.opts.fused_collectives must be auto, nccl, multimem or p2p; got %r" % (mode,))
+    out["fused_collectives"] = mode
     return out
+
+
+def resolve_collectives(mode, world_size):
+    """The transport ``auto`` stands for at a world size."""
+    if world_size <= 1:
+        return "none"
+    if mode == "auto":
+        return "p2p" if world_size <= 3 else "multimem"
+    return mode
 
 
 def build_loss_scaler(parsed, device=None):
@@ -82,7 +106,7 @@ class ChunkStepEngine(torch.nn.Module):
     slots the way the reference's backward hook does
     (patrickstar/core/hook.py:200-230)."""
 
-    def __init__(self, model, client, config):
+    def __init__(self, model, client, config, collectives=None):
         super().__init__()
         self.module = model
         self.client = client
@@ -95,6 +119,21 @@ class ChunkStepEngine(torch.nn.Module):
             gradient_clipping=self.gradient_clipping, lr=op["lr"], betas=op["betas"], eps=op["eps"],
             weight_decay=op["weight_decay"], use_adamw=(parsed["optim_type"] == "AdamW"),
             use_hybrid_adam=op["use_hybrid_adam"])
+        # how a data-parallel step exchanges chunks; the fused forms need the fp16 chunk list
+        # in symmetric memory
+        want = collectives or resolve_collectives(parsed["fused_collectives"], client.world_size)
+        if want in ("multimem", "p2p") and client.symm_handle is None:
+            want = "nccl"
+        self.collectives = want
+        # NCCL form: a group's reduce-scatter starts as soon as its gradients are complete
+        self.optimizer.rs_on_handoff = (want == "nccl")
+        # hand every chunk-managed gradient off the moment autograd has accumulated it, so
+        # that the overflow test, the copy into the slot and the reduce-scatter trigger run
+        # inside backward (patrickstar/core/hook.py:205-230)
+        self._hooks = []
+        for p in self.module.parameters():
+            if p.requires_grad and p.dtype == torch.float16:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self.optimizer.handoff_grad))
 
     def forward(self, *inputs, **kwargs):
         return self.module(*inputs, **kwargs)
@@ -107,7 +146,7 @@ class ChunkStepEngine(torch.nn.Module):
         else:
             loss.backward()
         for p in self.module.parameters():
-            self.optimizer.handoff_grad(p)   # overflow test + copy into the slot, one pass
+            self.optimizer.handoff_grad(p)   # whatever the hooks did not see (no-op otherwise)
         self._grads_scanned = True
 
     def step(self):
@@ -117,23 +156,52 @@ class ChunkStepEngine(torch.nn.Module):
         if self.client.world_size > 1:
             # data parallel: reduce-scatter of the gradient chunks, rank-local step,
             # all-gather of the param chunks (patrickstar/core/client.py:818-856, 428-497)
+            if self.collectives in ("multimem", "p2p"):
+                return self.optimizer.step_fused_collectives(self.collectives, scan="done" if scanned else "local")
             return self.optimizer.step_with_collectives(scan="done" if scanned else "local")
         return self.optimizer.step(scan=not scanned)
 
 
+def _client_for(parsed, local_rank, config):
+    """The chunk manager for a config: symmetric (NVSwitch multicast / peer-mapped)
+    fp16 memory when a fused transport is asked for.  Every rank must end up with
+    the same kind, so the ranks agree on whether the symmetric set-up worked."""
+    world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
+    want = resolve_collectives(parsed["fused_collectives"], world)
+    kw = dict(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
+              config=(config or {}).get("client", None))
+    return ChunkClient(symmetric=want in ("multimem", "p2p"), **kw), want
+
+
 def initialize_engine(model_func, local_rank, config=None, client=None):
     """runtime/__init__.py:40-93.  Returns ``(engine, optimizer)``."""
+    collectives = None
     if isinstance(model_func, torch.nn.Module):
         assert client is not None, "Must pass the client when passing a nn.Module."
         model = model_func
     else:
         assert callable(model_func), "model_func need to be callable."
         parsed = parse_config(config)
-        client = ChunkClient(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
-                             config=(config or {}).get("client", None))
+        client, collectives = _client_for(parsed, local_rank, config)
         model = model_func()
         model.to(dtype=torch.float16)
         client.register_module(model)
-        client.allocate()
-    engine = ChunkStepEngine(model=model, client=client, config=config)
+        try:
+            client.allocate()
+            ok = 1
+        except RuntimeError:
+            if not client.symmetric:
+                raise
+            ok = 0
+        if client.symmetric and client.world_size > 1:
+            t = torch.tensor([ok], dtype=torch.int32, device=client.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+            if int(t.item()) == 0:
+                # symmetric memory did not come up everywhere: plain memory, NCCL collectives
+                client = ChunkClient(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
+                                     config=(config or {}).get("client", None))
+                client.register_module(model)
+                client.allocate()
+                collectives = "nccl"
+    engine = ChunkStepEngine(model=model, client=client, config=config, collectives=collectives)
     return (engine, engine.optimizer)

@@ -20,6 +20,11 @@ Differences from the reference that a user can see
   * like the reference, hyper-parameters are captured into ``state[p]`` at
     construction (``:112-120``) and the step reads them from there, not from
     ``param_groups``.
+  * parameters registered with the client as torch-managed (the reference's
+    TORCH_BASED kind: fp32 parameter, fp32 gradient, no fp16 slot, ``:345-353``)
+    are updated by the same step, in their place of the visiting order, by one
+    extra launch over a table of them; like the reference their gradients are
+    neither tested for overflow nor divided by the world size.
 """
 import ctypes as C
 from copy import deepcopy
@@ -27,8 +32,8 @@ from copy import deepcopy
 import numpy as np
 import torch
 
-from ._lib import (CHUNK_DESC_DTYPE, PS_MAX_GROUPS, SEGMENT_DTYPE, GroupHyper, ScalerState, StepCtrl,
-                   StepPlan, check, lib)
+from ._lib import (CHUNK_DESC_DTYPE, PS_MAX_GROUPS, SEGMENT_DTYPE, TENSOR_DESC_DTYPE, GroupHyper, ScalerState,
+                   StepCtrl, StepPlan, check, lib)
 from .loss_scaler import DynamicLossScaler, _DeviceScaler
 from .timers import ADAM, ADAM_COMPUTE, ADAM_OFFLOAD, ADAM_OVERFLOW_SCAN, PhaseTimer
 
@@ -81,18 +86,38 @@ class FP16Adam(torch.optim.Optimizer):
         # eager state, as the reference (fp16_cpu_adam.py:112-120); the group
         # index of every tensor in the chunk layout follows param_groups
         name_of = {id(p): n for n, p in client.params.items()}
+        torch_name_of = {id(p): n for n, (p, _) in client.torch_params.items()}
         lay = client.layout
+        self._torch = []   # [name, param, group index, visiting position] of the torch-managed parameters
         for gi, group in enumerate(self.param_groups):
             for p in group["params"]:
-                if id(p) not in name_of:
+                if id(p) not in name_of and id(p) not in torch_name_of:
                     raise ValueError("FP16Adam got a parameter that is not registered with the client")
                 st = self.state[p]
                 st["betas"] = group["betas"]
                 st["lr"] = group["lr"]
                 st["weight_decay"] = group["weight_decay"]
                 st["eps"] = group["eps"]
+                if id(p) in torch_name_of:
+                    # fp16_cpu_adam.py:122-131: momentum and variance of a torch-managed
+                    # parameter are plain fp32 tensors of its shape
+                    name = torch_name_of[id(p)]
+                    st["name"] = name
+                    st["exp_avg"] = torch.zeros_like(p.data, dtype=torch.float32, device=self.device)
+                    st["exp_avg_sq"] = torch.zeros_like(p.data, dtype=torch.float32, device=self.device)
+                    self._torch.append([name, p, gi, client.torch_params[name][1]])
+                    continue
                 st["name"] = name_of[id(p)]
                 lay.set_group(name_of[id(p)], gi)
+        self._torch.sort(key=lambda t: t[3])
+        self._torch_table_dev = (torch.zeros(max(len(self._torch), 1) * TENSOR_DESC_DTYPE.itemsize,
+                                             dtype=torch.uint8, device=self.device) if self._torch else None)
+        # backward-side bookkeeping for data-parallel runs: elements handed off per
+        # communication group, and the reduce-scatters already fired for complete groups
+        self.rs_on_handoff = False
+        self._handed = {}
+        self._rs_fired = {}
+        self._expected = None
 
         # section timing of the step on CUDA events (off by default; no sync either way)
         self.time_profile = False
@@ -124,10 +149,29 @@ class FP16Adam(torch.optim.Optimizer):
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
+    def _call_sequence(self):
+        """The adam_update calls the reference would make on this rank in one step,
+        in its visiting order (the optimizer's parameter order, remote chunks
+        skipped; fp16_cpu_adam.py:569-606): ("chunk", piece) and ("torch", index
+        into self._torch) entries."""
+        c = self.client
+        seq = []
+        torch_left = list(range(len(self._torch)))
+        for piece in c.layout.calls_of_rank(c.rank):
+            while torch_left and self._torch[torch_left[0]][3] <= piece.tensor_index:
+                seq.append(("torch", torch_left.pop(0)))
+            seq.append(("chunk", piece))
+        seq.extend(("torch", i) for i in torch_left)
+        return seq
+
     def _build_tables(self):
         c = self.client
         lay = c.layout
-        local, numels, ranges, segs = lay.build_tables(c.rank)
+        seq = self._call_sequence()
+        # the first call of a step sees another beta^t than the later ones (slot 0); when a
+        # torch-managed parameter is visited first, no chunk piece carries that slot
+        torch_first = bool(seq) and seq[0][0] == "torch"
+        local, numels, ranges, segs = lay.build_tables(c.rank, first_call_slot=not torch_first)
         n_local = len(local)
         cs = lay.chunk_size
         desc = np.zeros(n_local, dtype=CHUNK_DESC_DTYPE)
@@ -154,8 +198,12 @@ class FP16Adam(torch.optim.Optimizer):
         self._n_local = n_local
         self._max_numel = int(max(numels)) if numels else 0
         self._max_numel_resident = int(max(numels[:n_res])) if n_res else 0
-        self._first_group, self._last_group, self._n_calls = lay.plan_groups(c.rank)
-        self._n_updated = int(sum(numels))
+        group_of = lambda e: e[1].group if e[0] == "chunk" else self._torch[e[1]][2]
+        self._first_group = group_of(seq[0]) if seq else 0
+        self._last_group = group_of(seq[-1]) if seq else 0
+        self._n_calls = len(seq)
+        self._torch_slots = [0 if (torch_first and i == seq[0][1]) else 1 + t[2] for i, t in enumerate(self._torch)]
+        self._n_updated = int(sum(numels)) + sum(t[1].numel() for t in self._torch)
 
     def _ensure_pow_table(self, upto):
         if upto < self._pow_len:
@@ -196,12 +244,27 @@ class FP16Adam(torch.optim.Optimizer):
 
     @torch.no_grad()
     def handoff_grad(self, param):
-        """The backward hook's per-parameter work (patrickstar/core/hook.py:212-216)
+        """The backward hook's per-parameter work (patrickstar/core/hook.py:205-230)
         as one kernel: test ``param.grad`` for inf/nan into the device flag and copy
         it into the parameter's fp16 slot, then drop ``param.grad``.  No host sync.
-        A step whose gradients all arrived this way may run with ``scan=False``."""
+        A step whose gradients all arrived this way may run with ``scan=False``.
+
+        With ``rs_on_handoff`` set (data parallel, NCCL form) the hand-off also
+        counts the elements that have arrived per communication group and, once a
+        group's gradients are complete, fires that group's reduce-scatter at once
+        on the reduce-scatter communicator — the reference's trigger
+        (hook.py:218-227 -> patrickstar/core/client.py:812-840) — so that the
+        collective overlaps the rest of backward; ``step_with_collectives(scan="done")``
+        then only waits for it.  Every rank must hand its gradients off in the same
+        order (same model, same graph), as NCCL requires of collectives.
+
+        A torch-managed (fp32) parameter keeps its ``.grad``: the step reads it
+        in place."""
         g = param.grad
         if g is None:
+            return
+        st_p = self.state[param]
+        if "exp_avg" in st_p:   # torch-managed: nothing to hand off
             return
         if g.dtype != torch.float16 or not g.is_cuda:
             raise TypeError("handoff_grad needs a CUDA fp16 gradient, got %s on %s" % (g.dtype, g.device))
@@ -211,6 +274,37 @@ class FP16Adam(torch.optim.Optimizer):
             check(lib.ps_grad_handoff(g.data_ptr(), param.data.data_ptr(), g.numel(), flag, self._stream()),
                   "ps_grad_handoff")
         param.grad = None
+        c = self.client
+        if self.rs_on_handoff and c.world_size > 1:
+            self._count_handoff(st_p["name"])
+
+    def _count_handoff(self, name):
+        c = self.client
+        lay = c.layout
+        cs, w = lay.chunk_size, c.world_size
+        if self._expected is None:
+            exp = {}
+            for t in lay.tensors:
+                self._spread(t, cs, w, exp)
+            self._expected = exp
+        got = {}
+        self._spread(lay.tensor(name), cs, w, got)
+        for g, n in got.items():
+            self._handed[g] = self._handed.get(g, 0) + n
+            if self._handed[g] == self._expected[g] and g not in self._rs_fired:
+                # the group's gradients are complete on this rank: reduce-scatter now
+                self._rs_fired[g] = c.reduce_scatter_group(g, async_op=True)
+
+    @staticmethod
+    def _spread(info, cs, w, acc):
+        """Add a tensor's elements to ``acc[communication group]``."""
+        pos, rest = info.flat_start(cs), info.numel
+        while rest > 0:
+            take = min(rest, cs - pos % cs)
+            g = (pos // cs) // w
+            acc[g] = acc.get(g, 0) + take
+            pos += take
+            rest -= take
 
     @torch.no_grad()
     def step(self, closure=None, grad_divisor=None, scan=True):
@@ -245,6 +339,7 @@ class FP16Adam(torch.optim.Optimizer):
             if tp:
                 self.timer.start_profile(ADAM_COMPUTE)
             self._update_resident(st)
+            self._update_torch_params(st)
             if tp:
                 self.timer.finish_profile(ADAM_COMPUTE)
             if self._offload is not None:
@@ -256,6 +351,56 @@ class FP16Adam(torch.optim.Optimizer):
             if tp:
                 self.timer.finish_profile(ADAM)
         return loss
+
+    def _update_torch_params(self, st):
+        """The torch-managed parameters' share of the step (fp16_cpu_adam.py:345-353):
+        one launch over a table of (param, fp32 grad, exp_avg, exp_avg_sq) rows that
+        is rebuilt every step because autograd hands out a new ``.grad`` each time.
+        Parameters without a gradient this step are left out, like every optimizer
+        does."""
+        if not self._torch:
+            return
+        rows = np.zeros(len(self._torch), dtype=TENSOR_DESC_DTYPE)
+        n = 0
+        for i, (name, p, gi, _) in enumerate(self._torch):
+            g = p.grad
+            if g is None:
+                continue
+            if g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous():
+                raise TypeError("torch-managed parameter %s needs a contiguous CUDA fp32 gradient" % name)
+            state = self.state[p]
+            rows[n] = (p.data.data_ptr(), g.data_ptr(), state["exp_avg"].data_ptr(),
+                       state["exp_avg_sq"].data_ptr(), p.numel(), self._torch_slots[i], 0)
+            n += 1
+        if n:
+            check(lib.ps_tensor_table_step(rows.ctypes.data, n, len(self.param_groups) + 1,
+                                           self._torch_table_dev.data_ptr(), self._ctrl.data_ptr(), st),
+                  "ps_tensor_table_step")
+
+    @torch.no_grad()
+    def restore_fp16(self):
+        """fp16 slot := half(fp32 master) for every resident local chunk, the
+        restore of has_overflow_and_reset_param (fp16_cpu_adam.py:298-309) on its
+        own (a skipped step does it by itself)."""
+        n = self.client.n_resident
+        if n:
+            with torch.cuda.device(self.device):
+                check(lib.ps_restore_fp16(self._desc_dev.data_ptr(), n, self._max_numel_resident,
+                                          self._segs_dev.data_ptr(), self._stream()), "ps_restore_fp16")
+
+    def rebalance(self, state_budget_bytes=None):
+        """Re-decide which local chunks keep their fp32 state in HBM from the memory
+        that is free now (``ChunkClient.rebalance``) and rebuild the device tables
+        and the offload pipeline when the split changed.  The reference re-derives
+        this before every step (fp16_cpu_adam.py:523-528); call it between steps."""
+        if not self.client.rebalance(state_budget_bytes):
+            return False
+        self._offload = None
+        self._build_tables()
+        if self.client.n_resident < len(self.client.local_ids):
+            from .offload import OffloadPipeline
+            self._offload = OffloadPipeline(self.client, self)
+        return True
 
     def _begin(self, grad_divisor, st):
         self._calls += 1
@@ -360,7 +505,9 @@ class FP16Adam(torch.optim.Optimizer):
                                                           self._scaler.flag_ptr, st), "ps_overflow_scan_buffer")
                     c.all_reduce_flag(self._scaler.flag_tensor)
                 self._begin(c.world_size, st)
-            rs = [c.reduce_scatter_group(g, async_op=True) for g in range(n_groups)]
+            # reduce-scatters already fired from the backward hand-off are only waited for
+            fired, self._rs_fired, self._handed = self._rs_fired, {}, {}
+            rs = [fired[g] if g in fired else c.reduce_scatter_group(g, async_op=True) for g in range(n_groups)]
             if scan == "reduced":
                 for g in range(n_groups):
                     rs[g].wait()  # stream-level wait, not a host block
@@ -388,12 +535,13 @@ class FP16Adam(torch.optim.Optimizer):
                 self._offload.run()
                 for g in range(n_res, n_groups):
                     ag.append(c.all_gather_group(g, async_op=True))
+            self._update_torch_params(st)
             for w in ag:
                 w.wait()
         return None
 
     @torch.no_grad()
-    def step_fused_collectives(self, transport="multimem"):
+    def step_fused_collectives(self, transport="multimem", scan="local"):
         """The multi-GPU chunk step as ONE kernel over NVSwitch multicast memory
         (needs ``ChunkClient(symmetric=True)``): the gradient of every owned
         element is loaded as the in-switch sum over all ranks' fp16 buffers — the
@@ -411,7 +559,13 @@ class FP16Adam(torch.optim.Optimizer):
         ``transport="multimem"``: in-switch reduction and multicast stores;
         ``transport="p2p"``: peer loads summed in fp32 in rank order and peer
         stores (exact single rounding, no multicast object needed, cheaper on
-        the links for 2-3 ranks, dearer for 8)."""
+        the links for 2-3 ranks, dearer for 8);
+        ``transport="staged"``: the multimem form as a two-kernel pipeline — a light
+        puller brings chunk k+1's reduced gradients into a local staging buffer
+        while the step kernel updates chunk k (same results bit for bit).
+
+        ``scan="done"``: the gradients were tested when they were handed over
+        (``handoff_grad``), so the scan of the whole fp16 buffer is left out."""
         c = self.client
         if c.world_size == 1:
             return self.step()
@@ -419,9 +573,12 @@ class FP16Adam(torch.optim.Optimizer):
             raise RuntimeError("step_fused_collectives needs ChunkClient(symmetric=True)")
         if self._offload is not None:
             raise NotImplementedError("fused collectives with offloaded chunks")
+        if scan not in ("local", "done"):
+            raise ValueError("scan must be 'local' or 'done'")
+        self._handed = {}
         with torch.cuda.device(self.device):
             st = self._stream()
-            if self._dynamic:
+            if self._dynamic and scan == "local":
                 check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(), self._scaler.flag_ptr, st),
                       "ps_overflow_scan_buffer")
             c.all_reduce_flag(self._scaler.flag_tensor)
@@ -435,8 +592,21 @@ class FP16Adam(torch.optim.Optimizer):
                 check(lib.ps_chunk_step_p2p(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
                                             self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
                                             c.peer_bases.data_ptr(), c.world_size, st), "ps_chunk_step_p2p")
+            elif transport == "staged":
+                if getattr(self, "_fused_pipe", None) is None:
+                    self._fused_pipe = C.c_void_p()
+                    check(lib.ps_fused_pipe_create(C.byref(self._fused_pipe)), "ps_fused_pipe_create")
+                    slot = (self._max_numel_resident + 7) // 8 * 8
+                    self._fused_staging = torch.empty(2 * slot, dtype=torch.float16, device=self.device)
+                check(lib.ps_chunk_step_fused_staged(self._fused_pipe, self._desc_dev.data_ptr(), c.n_resident,
+                                                     self._max_numel_resident, self._segs_dev.data_ptr(),
+                                                     self._ctrl.data_ptr(), c.fp16.data_ptr(),
+                                                     c.fp16_multicast_ptr, c.peer_bases.data_ptr(),
+                                                     c.world_size, self._fused_staging.data_ptr(), st),
+                      "ps_chunk_step_fused_staged")
             else:
-                raise ValueError("transport must be 'multimem' or 'p2p'")
+                raise ValueError("transport must be 'multimem', 'p2p' or 'staged'")
+            self._update_torch_params(st)
             if getattr(self, "_barrier_buf", None) is None:
                 self._barrier_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
             c.all_reduce_flag(self._barrier_buf)
@@ -461,6 +631,12 @@ class FP16Adam(torch.optim.Optimizer):
                                                        self._stream()), "ps_multimem_reduce_probe")
                 out.append(dst)
         return out
+
+    def __del__(self):
+        pipe = getattr(self, "_fused_pipe", None)
+        if pipe is not None and pipe.value:
+            lib.ps_fused_pipe_destroy(pipe)
+            self._fused_pipe = None
 
     # --------------------------------------------------------------- inspection
     def read_ctrl(self) -> StepCtrl:
@@ -502,6 +678,9 @@ class FP16Adam(torch.optim.Optimizer):
                 entry = {k: st[k] for k in ("betas", "lr", "weight_decay", "eps")}
                 entry["step"] = int(ctrl.step)
                 for kind in ("exp_avg", "exp_avg_sq"):
+                    if kind in st:   # torch-managed parameter: plain tensors
+                        entry[kind] = st[kind].detach().cpu().clone()
+                        continue
                     pieces = self.client.access_data(st["name"], kind)
                     numel = self.client.layout.tensor(st["name"]).numel
                     if pieces and sum(t.numel() for t, _ in pieces) == numel:
@@ -540,7 +719,9 @@ class FP16Adam(torch.optim.Optimizer):
                     st[k] = saved[k]
                 step = saved["step"] if step is None else step
                 for kind in ("exp_avg", "exp_avg_sq"):
-                    if kind in saved:
+                    if kind in saved and kind in st:
+                        st[kind].copy_(saved[kind])
+                    elif kind in saved:
                         flat = saved[kind].reshape(-1)
                         for t, off in self.client.access_data(st["name"], kind):
                             t.copy_(flat[off:off + t.numel()])

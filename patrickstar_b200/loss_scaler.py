@@ -19,6 +19,21 @@ def _stream_ptr(device):
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+class _ScaleByDeviceState(torch.autograd.Function):
+    """loss * cur_scale with the scale read on the device by the kernel
+    (``ps_scale_loss``): forward scales the loss, backward scales the incoming
+    gradient by the same factor.  fp32 CUDA tensors."""
+
+    @staticmethod
+    def forward(ctx, loss, scaler):
+        ctx.scaler = scaler
+        return scaler._scale_on_device(loss)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return ctx.scaler._scale_on_device(grad_out), None
+
+
 class _DeviceScaler:
     """Shared plumbing: the 64-byte ps_scaler_state block and the overflow flag."""
 
@@ -75,11 +90,27 @@ class _DeviceScaler:
         v = self.read_state().cur_scale
         return int(v) if float(v).is_integer() and self._int_scale else v
 
+    def _scale_on_device(self, x):
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        with torch.cuda.device(self.device):
+            check(lib.ps_scale_loss(x.data_ptr(), out.data_ptr(), x.numel(), self._state.data_ptr(),
+                                    _stream_ptr(self.device)), "ps_scale_loss")
+        return out
+
+    def scale_loss(self, loss):
+        """``loss * self.loss_scale`` as a differentiable device-side product: the
+        scale never travels to the host.  fp32 CUDA losses go through the
+        ``ps_scale_loss`` kernel; any other dtype is multiplied by the scale's
+        device tensor."""
+        if loss.is_cuda and loss.dtype == torch.float32 and loss.device == self.device:
+            return _ScaleByDeviceState.apply(loss, self)
+        return loss * self.scale_tensor.to(device=loss.device, dtype=loss.dtype)
+
     def backward(self, loss, retain_graph=False):
         """loss_scaler.py:188-190 — scaled backward; the scale is multiplied in on
         the device, without reading it back."""
-        scaled_loss = loss * self.scale_tensor.to(loss.dtype)
-        scaled_loss.backward(retain_graph=retain_graph)
+        self.scale_loss(loss).backward(retain_graph=retain_graph)
 
     def state_dict(self):
         st = self.read_state()

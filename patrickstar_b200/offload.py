@@ -4,10 +4,11 @@ launches) is native: ``ps_offload_step`` in ``csrc/ps_offload.cu``.
 
 The reference decides per step how many chunks fit on the GPU for Adam
 (``margin_chunk_num_for_gpu_adam``, patrickstar/ops/fp16_cpu_adam.py:523-528)
-and updates the others with its CPU Adam.  Here the split is fixed at
-allocation (``ChunkClient.allocate(state_budget_bytes=...)``): the first
-``n_resident`` local chunks stay in HBM, the others live in pinned host memory
-and are updated by the same GPU kernel through ``n_slots`` staging slots.
+and updates the others with its CPU Adam.  Here the split is decided at
+allocation (``ChunkClient.allocate(state_budget_bytes=...)``) and re-decided on
+request between steps (``FP16Adam.rebalance``): the first ``n_resident`` local
+chunks stay in HBM, the others live in pinned host memory and are updated by
+the same GPU kernel through ``n_slots`` staging slots.
 """
 import ctypes as C
 
@@ -61,6 +62,12 @@ class OffloadPipeline:
             check(lib.ps_table_check(base.ctypes.data, client.n_resident, optimizer._segs_host.ctypes.data,
                                      len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
                   "ps_table_check")
+        if rows:
+            # the piece rows too: biased state pointers, first element (`reserved`) and length
+            piece_rows = np.array(rows, dtype=CHUNK_DESC_DTYPE)
+            check(lib.ps_table_check(piece_rows.ctypes.data, len(piece_rows), optimizer._segs_host.ctypes.data,
+                                     len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
+                  "ps_table_check (offload pieces)")
         desc = np.concatenate([base, np.array(rows, dtype=CHUNK_DESC_DTYPE)]) if rows else base
         optimizer._desc_host = desc
         optimizer._desc_dev = torch.from_numpy(desc.view(np.uint8).copy()).to(dev)

@@ -27,9 +27,13 @@ def main():
     config = {"optimizer": {"type": "AdamW", "params": {"lr": 2e-3, "eps": 1e-6, "weight_decay": 0.01}},
               "fp16": {"enabled": True, "loss_scale": 0, "initial_scale_power": 8, "loss_scale_window": 1000,
                        "hysteresis": 2, "min_loss_scale": 1},
-              "default_chunk_size": 10240}
+              "default_chunk_size": 10240,
+              "client": {"opts": {"fused_collectives": os.environ.get("PS_TEST_COLLECTIVES", "auto")}}}
     engine, opt = initialize_engine(model_func, local, config)
     client = engine.client
+    want = config["client"]["opts"]["fused_collectives"]
+    assert engine.collectives == {"auto": "p2p" if world <= 3 else "multimem"}.get(want, want), engine.collectives
+    assert (client.symm_handle is not None) == (engine.collectives != "nccl")
     assert client.world_size == world and client.layout.n_chunks % world == 0
     assert client.layout.n_data_chunks >= 3      # several communication groups
     gen = torch.Generator(device=dev).manual_seed(100 + rank)   # a different batch on every rank
@@ -44,7 +48,15 @@ def main():
             loss = loss * float("inf")           # one rank overflows: every rank must skip
         losses.append(float(loss.detach()))
         engine.backward(loss)
+        if engine.collectives == "nccl":
+            # every communication group that holds parameters was reduce-scattered from the
+            # backward hand-off already; step() only waits for those
+            with_data = {c // world for c in range(client.layout.n_data_chunks)}
+            assert set(opt._rs_fired) == with_data, (sorted(opt._rs_fired), sorted(with_data))
+        else:
+            assert not opt._rs_fired
         engine.step()
+        assert not opt._rs_fired and not opt._handed
         # after the all-gather every rank holds the same fp16 parameters
         mine = client.fp16.clone()
         ref = mine.clone()

@@ -12,6 +12,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 SCAN = os.environ.get("PS_TEST_SCAN", "local")
+FUSED = ("fused", "p2p", "staged")          # one-kernel / two-kernel forms over symmetric memory
+TRANSPORT = {"fused": "multimem", "p2p": "p2p", "staged": "staged"}
 
 
 def main():
@@ -29,7 +31,7 @@ def main():
     cs = 1 << 15
     n_tensors = 3 * world + 1          # -> padded with dummy chunks
     client = ChunkClient(rank=local, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
-                         symmetric=(SCAN in ("fused", "p2p")))
+                         symmetric=(SCAN in FUSED))
     client.append_tensor_list([("w%d" % i, cs - (7 if i == n_tensors - 1 else 0), i % 2)
                                for i in range(n_tensors)])
     n_off = int(os.environ.get("PS_TEST_OFFLOAD", "0"))     # local chunks kept in pinned host memory
@@ -66,10 +68,10 @@ def main():
         dist.all_gather(allg, grads.to(dev))
         exact = sum(t.double() for t in allg)
         mag = sum(t.double().abs() for t in allg)
-        if SCAN in ("fused", "p2p"):
+        if SCAN in FUSED:
             # what the fused kernel's reduction returns for this rank's chunks
             dist.barrier()
-            reduced = opt.reduced_gradients("multimem" if SCAN == "fused" else "p2p")
+            reduced = opt.reduced_gradients("p2p" if SCAN == "p2p" else "multimem")
             torch.cuda.synchronize()
             dist.barrier()
         else:
@@ -85,7 +87,7 @@ def main():
             got = reduced[k]
             if not poisoned:
                 want = exact[c * cs:(c + 1) * cs]
-                if SCAN == "fused":
+                if SCAN in ("fused", "staged"):
                     # the switch accumulates in fp32 and converts the sum to fp16 by truncation
                     # (measured: errors up to 0.9 ulp, always toward zero): less than one fp16
                     # ulp of the exact sum, inside the (world - 1) / 2 ulp a ring of fp16
@@ -107,8 +109,8 @@ def main():
                                          "exact %r contributions %r" % (c, i, int(bad.sum()), float(got[i]), float(want[i]),
                                                                         [float(t[c * cs + i]) for t in allg]))
             H.append(got.cpu().numpy().copy())
-        if SCAN in ("fused", "p2p"):
-            opt.step_fused_collectives("multimem" if SCAN == "fused" else "p2p")
+        if SCAN in FUSED:
+            opt.step_fused_collectives(TRANSPORT[SCAN])
         else:
             opt.step_with_collectives(scan=SCAN)
         skipped = orc.step(H, P, M, V, overflow=poisoned)

@@ -114,3 +114,26 @@ def test_package_import_is_lazy_and_fails_loudly_without_library(tmp_path, monke
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "missing.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _lib._load()
+
+
+def test_table_check_looks_at_the_first_element_field(L):
+    """Host-only: ps_chunk_desc.reserved (first element of a piece) must be a
+    multiple of 2048 and lie below numel."""
+    d = np.zeros(1, dtype=L.CHUNK_DESC_DTYPE)
+    s = np.zeros(1, dtype=L.SEGMENT_DTYPE)
+    d["p32"], d["exp_avg"], d["exp_avg_sq"], d["h16"] = 256, 512, 768, 1024
+    d["numel"], d["seg_begin"], d["seg_end"] = 8192, 0, 1
+    s["start"], s["end"], s["slot"] = 0, 8192, 0
+    chk = lambda: L.lib.ps_table_check(d.ctypes.data, 1, s.ctypes.data, 1, 1, 8192)
+    assert chk() == 0
+    for bad in (1, 8, 2047, 2056, 8192, 10240):
+        d["reserved"] = bad
+        assert chk() == L.PS_ERR_TABLE, bad
+    for good in (0, 2048, 6144):
+        d["reserved"] = good
+        assert chk() == 0, good
+    # the allocation-free entry point takes whole chunks only and says so before it touches a device
+    d["reserved"] = 2048
+    slots = (L.HyperSlot * 1)()
+    rc = L.lib.ps_chunk_step_static(d.ctypes.data, 1, 8192, s.ctypes.data, 1, C.cast(slots, C.c_void_p), 1, 0, None)
+    assert rc == L.PS_ERR_TABLE

@@ -47,3 +47,18 @@ def test_errors_like_the_reference():
     assert parse_config({"fp16": {"enabled": True, "loss_scale": 512}})["scaler"] == ("static", 512)
     assert parse_config({"fp16": {"enabled": True, "loss_scale": 0}})["scaler"][1]["init_scale"] == 2 ** 16
     assert parse_config({"gradient_clipping": 1.0})["gradient_clipping"] == 1.0
+
+
+def test_collectives_key_under_client_opts():
+    """client.opts.fused_collectives chooses how a data-parallel step exchanges
+    chunks; "auto" resolves by world size."""
+    from patrickstar_b200.engine import resolve_collectives
+    assert parse_config(None)["fused_collectives"] == "auto"
+    assert parse_config({})["fused_collectives"] == "auto"
+    cfg = {"client": {"mem_tracer": {"margin_use_ratio": 0.7}, "opts": {"with_mem_saving_comm": False,
+                                                                      "fused_collectives": "nccl"}}}
+    assert parse_config(cfg)["fused_collectives"] == "nccl"
+    with pytest.raises(ValueError, match="fused_collectives"):
+        parse_config({"client": {"opts": {"fused_collectives": "ring"}}})
+    assert [resolve_collectives("auto", w) for w in (1, 2, 3, 4, 8)] == ["none", "p2p", "p2p", "multimem", "multimem"]
+    assert resolve_collectives("nccl", 8) == "nccl" and resolve_collectives("multimem", 2) == "multimem"

@@ -111,9 +111,16 @@ def test_no_writeback_and_fp32_grads(op, oracle_port, ghalf, adamw):
 
 def test_torch_adam_path_tolerance(op):
     """The reference's own test (unitest/test_ds_cpu_adam.py:141-155): max |diff|
-    < 1e-4 against the torch re-statement of FP16Adam.torch_adam_update."""
+    < 1e-4 against the torch re-statement of FP16Adam.torch_adam_update
+    (patrickstar/ops/fp16_cpu_adam.py:245-277).  Beside that bar the measured
+    distance is reported and bounded: the torch path divides by sqrt(bc2) where
+    the native path multiplies by 1/sqrt(bc2) and folds lr/bc1 differently, so the
+    two are a few ulp apart, not bit-equal (ATen arithmetic: parity at the ulp
+    level is measured here, not pinned)."""
     import math
+    from helpers import ulp_diff_f32
     dev = torch.device("cuda:0")
+    worst = {"p": [0.0, 0], "m": [0.0, 0], "v": [0.0, 0]}
     for use_adamw in (False, True):
         for shape in ((1023,), (1024, 32)):
             for grad_dtype in (torch.float, torch.half):
@@ -144,6 +151,12 @@ def test_torch_adam_path_tolerance(op):
                     assert (p - p2).abs().max() < 1e-4
                     assert (m - m2).abs().max() < 1e-4
                     assert (v - v2).abs().max() < 1e-4
+                    for name, a, b in (("p", p, p2), ("m", m, m2), ("v", v, v2)):
+                        worst[name][0] = max(worst[name][0], float((a - b).abs().max()))
+                        worst[name][1] = max(worst[name][1], ulp_diff_f32(a.cpu().numpy(), b.cpu().numpy()))
+    print("torch_adam_update vs native path, worst over 16 cases (max abs, max ulp): "
+          + ", ".join("%s %.3g / %d" % (k, a, u) for k, (a, u) in worst.items()))
+    assert worst["m"][0] <= 1e-6 and worst["v"][0] <= 1e-6 and worst["p"][0] <= 1e-6
 
 
 def test_error_codes(op):

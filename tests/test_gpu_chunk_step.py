@@ -269,6 +269,15 @@ def test_table_validation_rejects_bad_tables():
     s["slot"][1] = 2
     assert chk() == PS_ERR_TABLE  # slot out of range
     s["slot"][1] = 1
+    # `reserved` is the first element the kernel processes: a multiple of 2048 below numel
+    d["reserved"] = 8
+    assert chk() == PS_ERR_TABLE   # would start the 128-bit accesses off their alignment
+    d["reserved"] = 2048
+    assert chk() == PS_ERR_TABLE   # beyond numel (100)
+    d["numel"] = 4096
+    big = lambda: lib.ps_table_check(d.ctypes.data, 1, s.ctypes.data, 2, 2, 8192)
+    assert big() == 0              # a piece [2048, 4096) as the offload pipeline builds them
+    d["numel"], d["reserved"] = 100, 0
     d["h16"] = 1026
     assert chk() == PS_ERR_ALIGN
     d["h16"] = 0

@@ -28,12 +28,14 @@ def _free_gib():
 def test_dynamic_loss_scale_16_chunks_200_steps():
     """16 chunks x 64 Mi elements, DynamicLossScaler(2^3, window 1000, hysteresis
     key 2, min 1) as initialize_engine builds it, 200 steps, every 17th step a
-    seeded injection of 1-8 inf/nan into one random chunk.  All chunks receive
-    the same gradients.  Chunk 0 holds the first tensor the optimizer visits in
-    a step, which sees another beta^t than the later ones
-    (patrickstar/ops/csrc/includes/cpu_adam.h:143-162); chunks 1..15 must stay
-    bit-identical to each other.  Chunks 0 and 1 are followed by the oracle for
-    all 200 steps."""
+    seeded injection of 1-8 inf/nan into one random chunk.  Every chunk has its
+    own state and receives its own gradients every step.  Four chunks spread over
+    the table are followed by the oracle for all 200 steps, bit for bit: the first
+    (its tensor makes the first adam_update call of a step, which sees another
+    beta^t than the later ones, patrickstar/ops/csrc/includes/cpu_adam.h:143-162),
+    the victim of the first injection, one mid-table chunk and the last.  As an
+    extra, chunks 6 and 7 are given identical states and gradients and must stay
+    bit-identical to each other; all chunks must end with fp16 == half(master)."""
     if _free_gib() < 24:
         pytest.skip("needs ~20 GiB of free device memory")
     from patrickstar_b200 import ChunkClient, FP16Adam
@@ -52,64 +54,86 @@ def test_dynamic_loss_scale_16_chunks_200_steps():
     op = parsed["optim_params"]
     opt = FP16Adam(client, client.params.values(), loss_scaler=scaler, lr=op["lr"], betas=op["betas"],
                    eps=op["eps"], weight_decay=op["weight_decay"], use_adamw=False)
+    # the injection plan is drawn up front so that the first victim can be followed
+    rng = np.random.RandomState(0)
+    plan = {}
+    for step in range(steps):
+        if step % 17 == 16:
+            victim = int(rng.randint(n_chunks))
+            where = [int(x) for x in rng.randint(0, CHUNK, size=rng.randint(1, 9))]
+            what = [float(rng.choice([np.inf, -np.inf, np.nan])) for _ in where]
+            plan[step] = (victim, where, what)
+    first_victim = plan[16][0]
+    followed = sorted({0, first_victim if first_victim not in (0, 15) else 3, 9 if first_victim != 9 else 10, 15})
+    assert len(followed) == 4
     gen = torch.Generator(device=DEV).manual_seed(0)
-    p0 = torch.empty(CHUNK, device=DEV).normal_(0, 0.02, generator=gen)
-    m0 = torch.empty(CHUNK, device=DEV).normal_(0, 1e-4, generator=gen)
-    v0 = torch.empty(CHUNK, device=DEV).normal_(0, 1e-6, generator=gen).abs_()
+    P, M, V = {}, {}, {}
     for k in range(n_chunks):
         p, m, v = client.chunk_state(k)
-        p.copy_(p0), m.copy_(m0), v.copy_(v0)
-    P = [p0.cpu().numpy(), p0.cpu().numpy()]
-    M = [m0.cpu().numpy(), m0.cpu().numpy()]
-    V = [v0.cpu().numpy(), v0.cpu().numpy()]
-    del p0, m0, v0
+        p.normal_(0, 0.02, generator=gen)
+        m.normal_(0, 1e-4, generator=gen)
+        v.normal_(0, 1e-6, generator=gen).abs_()
+        if k == 7:
+            for dst, src in zip((p, m, v), client.chunk_state(6)):
+                dst.copy_(src)
+        if k in followed:
+            P[k], M[k], V[k] = p.cpu().numpy(), m.cpu().numpy(), v.cpu().numpy()
     so = DynamicScalerOracle(2 ** 3, 2, 1000, 1)
-    # the oracle follows the first two of the 16 tensors; the others only matter through the
-    # beta^t history they leave in the optimizer object (trailing_call_group)
-    orc = StepOracle([(0, 0, CHUNK, 0), (1, 0, CHUNK, 0)],
-                     [{"lr": 1e-3, "betas": (0.9, 0.999), "eps": 1e-6, "weight_decay": 0}],
-                     so, False, trailing_call_group=0)
-    rng = np.random.RandomState(0)
-    pinned = torch.empty(CHUNK, dtype=torch.float16).pin_memory()
-    second = np.empty(CHUNK, dtype=np.float16)
+    # the oracle makes the followed tensors' adam_update calls in visiting order; the calls in
+    # between only repeat what the second call already leaves in the optimizer object's beta^t
+    # history, and the last followed tensor is the rank's last one
+    orc = StepOracle([(i, 0, CHUNK, 0) for i in range(len(followed))],
+                     [{"lr": 1e-3, "betas": (0.9, 0.999), "eps": 1e-6, "weight_decay": 0}], so, False)
+    pinned = [torch.empty(CHUNK, dtype=torch.float16).pin_memory() for _ in followed]
     tmp = torch.empty(CHUNK, device=DEV)
     skips = []
     for step in range(steps):
-        tmp.normal_(0, 1e-3, generator=gen).mul_(float(so.loss_scale))
-        g = tmp.half()
         for cid in range(n_chunks):
-            client.fp16_chunk(cid).copy_(g)
-        inject = step % 17 == 16
+            if cid == 7:
+                client.fp16_chunk(7).copy_(client.fp16_chunk(6))
+                continue
+            tmp.normal_(0, 1e-3, generator=gen).mul_(float(so.loss_scale))
+            client.fp16_chunk(cid).copy_(tmp)      # fp32 -> fp16, round to nearest even
+        inject = step in plan
         if inject:
-            victim = int(rng.randint(n_chunks))
-            for pos in rng.randint(0, CHUNK, size=rng.randint(1, 9)):
-                client.fp16_chunk(victim)[int(pos)] = float(rng.choice([np.inf, -np.inf, np.nan]))
-        pinned.copy_(g)
+            victim, where, what = plan[step]
+            for pos, val in zip(where, what):
+                client.fp16_chunk(victim)[pos] = val
+            if victim == 6:
+                client.fp16_chunk(7).copy_(client.fp16_chunk(6))
+        for buf, k in zip(pinned, followed):
+            buf.copy_(client.fp16_chunk(k))
         torch.cuda.synchronize()
-        second[:] = pinned.numpy()
-        H = [pinned.numpy(), second]
+        H = [buf.numpy() for buf in pinned]
         opt.step()
-        skipped = orc.step(H, P, M, V, overflow=inject)
+        skipped = orc.step(H, [P[k] for k in followed], [M[k] for k in followed], [V[k] for k in followed],
+                           overflow=inject)
         skips.append(skipped)
         st = scaler.read_state()  # bit-exact scale trajectory, every step
         assert (st.cur_scale, st.cur_iter, st.last_overflow_iter, st.cur_hysteresis) == \
             (float(so.cur_scale), so.cur_iter, so.last_overflow_iter, so.cur_hysteresis), step
         assert opt.read_ctrl().skip == int(inject), step
+        if step in (0, 16, 17, 100):   # early divergence would show here, not only at the end
+            for i, k in enumerate(followed):
+                assert n_bit_mismatch(client.chunk_state(k)[0].cpu().numpy(), P[k]) == 0, (step, k)
+                assert n_bit_mismatch(client.fp16_chunk(k).cpu().numpy(), H[i]) == 0, (step, k)
     assert sum(skips) == 11 and opt.step_count == steps - 11 == orc.step_count
     assert scaler.loss_scale == 1  # 8 -> 4 -> 2 -> 1, then pinned at min_scale
     torch.cuda.synchronize()
-    for k in (0, 1):
+    for i, k in enumerate(followed):
         p, m, v = client.chunk_state(k)
         assert n_bit_mismatch(p.cpu().numpy(), P[k]) == 0, k
         assert n_bit_mismatch(m.cpu().numpy(), M[k]) == 0, k
         assert n_bit_mismatch(v.cpu().numpy(), V[k]) == 0, k
-        assert n_bit_mismatch(client.fp16_chunk(k).cpu().numpy(), H[k]) == 0, k
-    p, m, v = client.chunk_state(1)
-    ref = [checksum(t) for t in (p, m, v, client.fp16_chunk(1))]
-    for k in range(2, n_chunks):
-        pk, mk, vk = client.chunk_state(k)
-        assert [checksum(t) for t in (pk, mk, vk, client.fp16_chunk(k))] == ref, k
-    assert [checksum(t) for t in client.chunk_state(0)] != ref[:3]  # the first-call quirk is real
+        assert n_bit_mismatch(client.fp16_chunk(k).cpu().numpy(), H[i]) == 0, k
+    six = [checksum(t) for t in (*client.chunk_state(6), client.fp16_chunk(6))]
+    seven = [checksum(t) for t in (*client.chunk_state(7), client.fp16_chunk(7))]
+    assert six == seven
+    sums = {tuple(checksum(client.chunk_state(k)[0])) for k in range(n_chunks)}
+    assert len(sums) == n_chunks - 1      # every chunk went its own way (6 and 7 together)
+    for k in range(n_chunks):
+        p = client.chunk_state(k)[0]
+        assert torch.equal(client.fp16_chunk(k).view(torch.int16), p.half().view(torch.int16)), k
 
 
 def test_gpt2_xl_layout_adamw_two_groups():

@@ -94,6 +94,19 @@ def test_static_variant_matches_regular_entry_point_twice():
             gs[0][123] = float("nan")
         return gs
 
+    # Nothing may be allocated by the two calls below: neither through torch's pool
+    # (memory_allocated / memory_reserved) nor behind its back (cudaMemGetInfo).  The
+    # first-call set-up (symbol address look-up) is made here, before the baseline.
+    warm_d, warm_s = _tables([(A[0][0], A[0][1], A[0][2], A[0][3], 0, 0, 0)], [(0, 1, 0)])
+    warm_slots = (L.HyperSlot * 1)()
+    L.check(lib.ps_chunk_step_static(warm_d.ctypes.data, 1, 16, warm_s.ctypes.data, 1,
+                                     C.cast(warm_slots, C.c_void_p), 1, 1, stream), "warm-up")
+    torch.cuda.synchronize()
+    seen = []
+
+    def mem_probe():
+        return (torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV), torch.cuda.mem_get_info(DEV)[0])
+
     # ---- call 1: three chunks, two groups, ragged segments ---------------------
     segs1 = [(0, 20001, 0), (20001, 49999, 2),      # chunk 0 (first piece -> slot 0)
              (0, 7, 2), (7, 50000, 1),               # chunk 1
@@ -109,9 +122,18 @@ def test_static_variant_matches_regular_entry_point_twice():
     assert ctrl.skip == 0 and ctrl.step == 1
     dB, sB = _tables([(B[k][0], B[k][1], B[k][2], B[k][3], numels1[k], *ranges1[k]) for k in range(3)], segs1)
     slots = (L.HyperSlot * 3)(*[ctrl.slots[i] for i in range(3)])
-    L.check(lib.ps_chunk_step_static(dB.ctypes.data, 3, max(numels1), sB.ctypes.data, len(segs1),
-                                     C.cast(slots, C.c_void_p), 3, 0, stream), "ps_chunk_step_static")
+    # tables in PINNED host memory, overwritten the moment the call returns: the entry point
+    # must have taken its copy by then (a caller with its own pool keeps tables pinned)
+    dB_pin = torch.from_numpy(dB.view(np.uint8).copy()).pin_memory()
+    sB_pin = torch.from_numpy(sB.view(np.uint8).copy()).pin_memory()
+    slots_pin = torch.frombuffer(bytearray(bytes(slots)), dtype=torch.uint8).pin_memory()
     torch.cuda.synchronize()
+    before = mem_probe()
+    L.check(lib.ps_chunk_step_static(dB_pin.data_ptr(), 3, max(numels1), sB_pin.data_ptr(), len(segs1),
+                                     slots_pin.data_ptr(), 3, 0, stream), "ps_chunk_step_static")
+    dB_pin.fill_(0xFF), sB_pin.fill_(0xFF), slots_pin.fill_(0xFF)
+    torch.cuda.synchronize()
+    seen.append((before, mem_probe()))
     for k in range(3):
         for j in range(4):
             assert torch.equal(A[k][j].view(torch.uint8), B[k][j].view(torch.uint8)), ("call 1", k, j)
@@ -131,10 +153,13 @@ def test_static_variant_matches_regular_entry_point_twice():
     ctrl = _regular_step(lib, L, dA, sA, max(numels2), plan, ctrl_dev, scaler_dev, flag_dev, pow_dev, 64, stream)
     assert ctrl.skip == 1 and ctrl.step == 1  # the poisoned step is skipped
     dB, sB = _tables([(B[k][0], B[k][1], B[k][2], B[k][3], numels2[k], *ranges2[k]) for k in range(2)], segs2)
+    torch.cuda.synchronize()
+    before = mem_probe()
     L.check(lib.ps_chunk_step_static(dB.ctypes.data, 2, max(numels2), sB.ctypes.data, len(segs2),
                                      C.cast(slots, C.c_void_p), 3, int(ctrl.skip), stream),
             "ps_chunk_step_static")
     torch.cuda.synchronize()
+    seen.append((before, mem_probe()))
     for k in range(3):
         for j in range(4):
             assert torch.equal(A[k][j].view(torch.uint8), B[k][j].view(torch.uint8)), ("call 2", k, j)
@@ -142,6 +167,10 @@ def test_static_variant_matches_regular_entry_point_twice():
     assert torch.equal(B[0][3].view(torch.int16), B[0][0].half().view(torch.int16))
     assert torch.equal(B[1][3][8:30000].view(torch.int16), B[1][0][8:30000].half().view(torch.int16))
     assert torch.isnan(gs[0][123]) and not torch.isnan(B[0][3][123])
+    # the property in the entry point's name: no device memory appeared or went away
+    for before, after in seen:
+        assert after[0] == before[0] and after[1] == before[1], (before, after)
+        assert after[2] >= before[2], ("free device memory shrank across the call", before, after)
 
 
 def test_static_variant_rejects_sizes_beyond_its_maximum():
