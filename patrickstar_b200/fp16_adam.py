@@ -121,6 +121,9 @@ class FP16Adam(torch.optim.Optimizer):
 
         # section timing of the step on CUDA events (off by default; no sync either way)
         self.time_profile = False
+        # optional callable(name): called between the phases of the fused multi-GPU step so that
+        # a benchmark can drop CUDA events there ("scan", "flag", "kernel", "barrier" = phase done)
+        self.phase_marker = None
         self.timer = PhaseTimer()
         self._calls = 0            # number of step() calls, an upper bound of the step counter
         self._pow_len = 0
@@ -576,13 +579,16 @@ class FP16Adam(torch.optim.Optimizer):
         if scan not in ("local", "done"):
             raise ValueError("scan must be 'local' or 'done'")
         self._handed = {}
+        mark = self.phase_marker or (lambda name: None)
         with torch.cuda.device(self.device):
             st = self._stream()
             if self._dynamic and scan == "local":
                 check(lib.ps_overflow_scan_buffer(c.fp16.data_ptr(), c.fp16.numel(), self._scaler.flag_ptr, st),
                       "ps_overflow_scan_buffer")
+            mark("scan")
             c.all_reduce_flag(self._scaler.flag_tensor)
             self._begin(c.world_size, st)
+            mark("flag")
             if transport == "multimem":
                 check(lib.ps_chunk_step_fused(self._desc_dev.data_ptr(), c.n_resident, self._max_numel_resident,
                                               self._segs_dev.data_ptr(), self._ctrl.data_ptr(), c.fp16.data_ptr(),
@@ -607,20 +613,25 @@ class FP16Adam(torch.optim.Optimizer):
             else:
                 raise ValueError("transport must be 'multimem', 'p2p' or 'staged'")
             self._update_torch_params(st)
+            mark("kernel")
             if getattr(self, "_barrier_buf", None) is None:
                 self._barrier_buf = torch.zeros(1, dtype=torch.int32, device=self.device)
             c.all_reduce_flag(self._barrier_buf)
+            mark("barrier")
         return None
 
-    def reduced_gradients(self, transport="multimem"):
+    def reduced_gradients(self, transport="multimem", only=None):
         """What the fused kernel loads as gradients: per owned chunk the sum of all
         ranks' fp16 slots, in-switch ("multimem") or fp32-accumulated over peer
-        loads ("p2p") (for tests; call between two barriers)."""
+        loads ("p2p") (for tests; call between two barriers).  ``only``: local
+        chunk indices to probe (default all)."""
         c = self.client
         cs = c.layout.chunk_size
         out = []
         with torch.cuda.device(self.device):
-            for cid in c.local_ids:
+            for k, cid in enumerate(c.local_ids):
+                if only is not None and k not in only:
+                    continue
                 dst = torch.empty(cs, dtype=torch.float16, device=self.device)
                 if transport == "p2p":
                     check(lib.ps_p2p_reduce_probe(c.fp16.data_ptr() + 2 * cid * cs, c.fp16.data_ptr(),

@@ -156,7 +156,9 @@ def test_torch_adam_path_tolerance(op):
                         worst[name][1] = max(worst[name][1], ulp_diff_f32(a.cpu().numpy(), b.cpu().numpy()))
     print("torch_adam_update vs native path, worst over 16 cases (max abs, max ulp): "
           + ", ".join("%s %.3g / %d" % (k, a, u) for k, (a, u) in worst.items()))
-    assert worst["m"][0] <= 1e-6 and worst["v"][0] <= 1e-6 and worst["p"][0] <= 1e-6
+    # (p is larger than m and v: with p, g in [0, 1) the first step moves p by up to 0.1 * m / sqrt(v),
+    # several units, so one ulp of the update is ~1e-6)
+    assert worst["m"][0] <= 1.2e-7 and worst["v"][0] <= 1.2e-7 and worst["p"][0] <= 4e-6
 
 
 def test_error_codes(op):
