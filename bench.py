@@ -85,6 +85,17 @@ def parse_args():
                     help="keep the fp32 state of this many of the rank's chunks in pinned host memory and "
                          "stream them through the double-buffered offload pipeline (hybrid placement); "
                          "prints the offload report instead of the headline line")
+    ap.add_argument("--config4-min-gpus", type=int, default=8,
+                    help="development: run the config4 leg from this many GPUs on (it is stated for 8)")
+    ap.add_argument("--config4-layout", default="gpt_40b", choices=["gpt_12b", "gpt_40b"],
+                    help="development: chunk list of the config4 leg")
+    ap.add_argument("--config4-budget-gb", type=float, default=40.0,
+                    help="per-GPU budget for fp32 master / momentum / variance in HBM in the config4 leg")
+    ap.add_argument("--handoff-overlap", action="store_true",
+                    help="N > 1, NCCL form: times a stand-in backward (one matmul per parameter, then the "
+                         "gradient hand-off) followed by the step, with each communication group's "
+                         "reduce-scatter fired from the hand-off and with all of them issued at step(); prints "
+                         "that report instead of the headline line")
     ap.add_argument("--offload-slots", type=int, default=2)
     ap.add_argument("--offload-piece", type=int, default=16 * 1024 * 1024, help="elements per staged piece")
     return ap.parse_args()
@@ -891,10 +902,15 @@ def run_config4(args, world, rank, local_rank, dev):
     between each group's reduce-scatter and all-gather."""
     import torch
     cs = args.chunk_size
-    if world < 8:
+    if world < args.config4_min_gpus:
         return {"omitted": "the configuration is stated for 8 GPUs"}
-    budget = 40 * 10 ** 9
-    n_total = 583
+    budget = int(args.config4_budget_gb * 10 ** 9)
+    from patrickstar_b200.chunk_list import ChunkLayout
+    from patrickstar_b200.model_layouts import model_specs
+    import numpy as np
+    probe = ChunkLayout(cs, world, "flat")
+    probe.append_tensor_list([(n, int(np.prod(sh)), g) for n, sh, g in model_specs(args.config4_layout)])
+    n_total = probe.n_data_chunks      # 583 for the 40B model at 64 Mi
     per_rank = (n_total + world - 1) // world
     n_res = min(per_rank, budget // (12 * cs))
     pinned_need = (per_rank - n_res) * 12 * cs
@@ -906,7 +922,7 @@ def run_config4(args, world, rank, local_rank, dev):
     if not agree(world, dev, host_ok and free > dev_need):
         return {"omitted": "not enough memory on this box: %.0f GiB of pinned host memory and %.0f GiB per GPU needed"
                            % (pinned_need * world / 2 ** 30, dev_need / 2 ** 30)}
-    w = Workload(args, "gpt_40b", world, rank, local_rank, dev, "nccl", budget=budget, seed=4000)
+    w = Workload(args, args.config4_layout, world, rank, local_rank, dev, "nccl", budget=budget, seed=4000)
     assert w.client.n_resident == n_res, (w.client.n_resident, n_res)
     parity = workload_parity_leg(w)
     steps = 3
@@ -1074,7 +1090,7 @@ def run_ours(args):
             extras["config2"] = run_config2(args, world, rank, local_rank, dev)
         else:
             extras["config3"] = run_config3(args, world, rank, local_rank, dev, args.collectives)
-            if world >= 8:
+            if world >= args.config4_min_gpus:
                 extras["config4"] = run_config4(args, world, rank, local_rank, dev)
 
     bad_parity = [p for p in ([parity] + [v.get("multi_gpu_parity") for v in extras.values()]) if p is not None
@@ -1233,8 +1249,84 @@ def run_offload(args):
         dist.destroy_process_group()
 
 
+def run_handoff_overlap(args):
+    """How much of the reduce-scatter time hides behind backward when a communication group's
+    reduce-scatter is fired the moment its last gradient is handed off
+    (patrickstar/core/hook.py:205-230 -> patrickstar/core/client.py:812-840) instead of at step().
+    Backward is played by one bf16 matmul per parameter (its "backward compute") followed by
+    FP16Adam.handoff_grad, parameters visited last to first."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--handoff-overlap needs torch.distributed.run with 2 or more ranks")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+    w = Workload(args, "uniform", world, rank, local_rank, dev, "nccl", npr=args.chunks)
+    client, opt, cs = w.client, w.opt, w.cs
+    params = list(client.params.values())[::-1]
+    grad_src = w.pristine[:cs]
+    a = torch.randn(8192, 8192, dtype=torch.bfloat16, device=dev)
+    c = torch.empty_like(a)
+
+    def backward_and_step(trigger, compute=True):
+        opt.rs_on_handoff = trigger
+        for p in params:
+            if compute:
+                torch.matmul(a, a, out=c)
+            p.grad = grad_src.view(p.shape)
+            opt.handoff_grad(p)
+        opt.step_with_collectives(scan="done")
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        ev = []
+        for _ in range(n):
+            dist.barrier()
+            x, y = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x.record()
+            fn()
+            y.record()
+            ev.append((x, y))
+        torch.cuda.synchronize()
+        return w.max_over_ranks(sum(x.elapsed_time(y) for x, y in ev) / n)
+
+    n = max(3, min(args.steps, 10))
+    at_step = timed(lambda: backward_and_step(False), n)
+    from_handoff = timed(lambda: backward_and_step(True), n)
+
+    def compute_only():
+        for _ in params:
+            torch.matmul(a, a, out=c)
+
+    def rs_only():
+        for wk in [client.reduce_scatter_group(g, async_op=True) for g in range(w.n_groups)]:
+            wk.wait()
+
+    compute_ms, rs_ms = timed(compute_only, n), timed(rs_only, n)
+    ctrl = opt.read_ctrl()
+    if rank == 0:
+        print(json.dumps({
+            "workload": "stand-in backward (one 8192^3 bf16 matmul per parameter, %d parameters = chunks of %d "
+                        "elements, last to first) + gradient hand-off + step with NCCL collectives, %d ranks"
+                        % (len(params), cs, world),
+            "ms_reduce_scatter_issued_at_step": at_step, "ms_reduce_scatter_fired_from_handoff": from_handoff,
+            "ms_backward_compute_alone": compute_ms, "ms_all_reduce_scatters_alone": rs_ms,
+            "reduce_scatter_time_hidden_ms": at_step - from_handoff,
+            "reduce_scatter_time_hidden_frac": (at_step - from_handoff) / rs_ms,
+            "skipped_steps": int(ctrl.n_skipped), "n_gpus": world, "repeats": n, "data": "synthetic"}))
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
+    if args.handoff_overlap:
+        return run_handoff_overlap(args)
     if args.offload_chunks > 0:
         return run_offload(args)
     if args.impl == "reference":

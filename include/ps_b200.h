@@ -191,6 +191,15 @@ int ps_adam_get_state(int optimizer_id, float out[4], uint64_t* step);
 int ps_table_check(const ps_chunk_desc* chunks_host, uint32_t n_chunks, const ps_segment* segs_host,
                    uint32_t n_segs, uint32_t n_slots, uint32_t chunk_capacity);
 
+/* Host-side validation of descriptors that cover a PIECE [reserved, numel) of a
+ * chunk (the offload pipeline's rows, see ps_offload_chunk): non-null 16-byte
+ * aligned bases, reserved a multiple of 2048 and below numel <= chunk_capacity,
+ * a non-empty segment range inside the table.  The segments are the whole
+ * chunk's (already validated with ps_table_check) and may reach beyond the
+ * piece; the kernel clips them to [reserved, numel). */
+int ps_piece_table_check(const ps_chunk_desc* pieces_host, uint32_t n_pieces, uint32_t n_segs,
+                         uint32_t chunk_capacity);
+
 /* Host-only helper: out[2*i] = float(pow(double(beta1), t0+i)), out[2*i+1] the
  * same for beta2 — the values IncrementStep's pow branch produces
  * (cpu_adam.h:147-156).  The step-begin kernel looks them up by the

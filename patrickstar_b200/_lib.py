@@ -101,6 +101,7 @@ SIGNATURES = {
                                  C.c_float, C.c_int, _p, _p, _p, _p, C.c_size_t, C.c_int, C.c_float,
                                  _p, _p]),
     "ps_table_check": (C.c_int, [_p, C.c_uint32, _p, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "ps_piece_table_check": (C.c_int, [_p, C.c_uint32, C.c_uint32, C.c_uint32]),
     "ps_pow_table_fill": (C.c_int, [C.c_float, C.c_float, C.c_uint64, C.c_uint64, _p]),
     "ps_ctrl_init": (C.c_int, [_p, C.c_uint64, C.c_float, C.c_float, _p]),
     "ps_scaler_init": (C.c_int, [_p, C.POINTER(ScalerState), _p]),

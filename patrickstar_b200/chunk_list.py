@@ -190,6 +190,22 @@ class ChunkLayout:
     def tensor(self, name) -> TensorInfo:
         return self._by_name[name]
 
+    def add_to_comm_groups(self, info: TensorInfo, acc: dict):
+        """Add a tensor's elements to ``acc[communication group]``, cut at chunk
+        boundaries (a tensor may straddle chunks and groups).  Summed over all
+        tensors this is the number of gradient elements a group must have received
+        before its reduce-scatter may start (patrickstar/core/client.py:793-817
+        waits for every tensor of the group's chunks to be HOLD_AFTER_BWD)."""
+        cs, w = self.chunk_size, self.world_size
+        pos, rest = info.flat_start(cs), info.numel
+        while rest > 0:
+            take = min(rest, cs - pos % cs)
+            g = (pos // cs) // w
+            acc[g] = acc.get(g, 0) + take
+            pos += take
+            rest -= take
+        return acc
+
     def total_numel(self):
         return sum(t.numel for t in self.tensors)
 

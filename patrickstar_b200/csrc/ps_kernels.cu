@@ -1820,6 +1820,22 @@ int ps_table_check(const ps_chunk_desc* chunks, uint32_t n_chunks, const ps_segm
     return PS_OK;
 }
 
+int ps_piece_table_check(const ps_chunk_desc* pieces, uint32_t n_pieces, uint32_t n_segs, uint32_t chunk_capacity)
+{
+    if (n_pieces > 0 && pieces == nullptr) return PS_ERR_INVALID;
+    if (chunk_capacity >= 0x7fffff00u) return PS_ERR_LIMIT;
+    for (uint32_t i = 0; i < n_pieces; ++i) {
+        const ps_chunk_desc& d = pieces[i];
+        if (!d.p32 || !d.exp_avg || !d.exp_avg_sq || !d.h16) return PS_ERR_INVALID;
+        if (!aligned16(d.p32) || !aligned16(d.exp_avg) || !aligned16(d.exp_avg_sq) || !aligned16(d.h16))
+            return PS_ERR_ALIGN;
+        if (d.numel > chunk_capacity) return PS_ERR_TABLE;
+        if (d.reserved % 2048u != 0u || d.reserved >= d.numel) return PS_ERR_TABLE;
+        if (d.seg_begin >= d.seg_end || d.seg_end > n_segs) return PS_ERR_TABLE;
+    }
+    return PS_OK;
+}
+
 int ps_pow_table_fill(float beta1, float beta2, uint64_t t0, uint64_t count, float* out_host)
 {
     if (count > 0 && out_host == nullptr) return PS_ERR_INVALID;

@@ -284,30 +284,16 @@ class FP16Adam(torch.optim.Optimizer):
     def _count_handoff(self, name):
         c = self.client
         lay = c.layout
-        cs, w = lay.chunk_size, c.world_size
         if self._expected is None:
             exp = {}
             for t in lay.tensors:
-                self._spread(t, cs, w, exp)
+                lay.add_to_comm_groups(t, exp)
             self._expected = exp
-        got = {}
-        self._spread(lay.tensor(name), cs, w, got)
-        for g, n in got.items():
+        for g, n in lay.add_to_comm_groups(lay.tensor(name), {}).items():
             self._handed[g] = self._handed.get(g, 0) + n
             if self._handed[g] == self._expected[g] and g not in self._rs_fired:
                 # the group's gradients are complete on this rank: reduce-scatter now
                 self._rs_fired[g] = c.reduce_scatter_group(g, async_op=True)
-
-    @staticmethod
-    def _spread(info, cs, w, acc):
-        """Add a tensor's elements to ``acc[communication group]``."""
-        pos, rest = info.flat_start(cs), info.numel
-        while rest > 0:
-            take = min(rest, cs - pos % cs)
-            g = (pos // cs) // w
-            acc[g] = acc.get(g, 0) + take
-            pos += take
-            rest -= take
 
     @torch.no_grad()
     def step(self, closure=None, grad_divisor=None, scan=True):

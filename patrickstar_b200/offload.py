@@ -65,9 +65,8 @@ class OffloadPipeline:
         if rows:
             # the piece rows too: biased state pointers, first element (`reserved`) and length
             piece_rows = np.array(rows, dtype=CHUNK_DESC_DTYPE)
-            check(lib.ps_table_check(piece_rows.ctypes.data, len(piece_rows), optimizer._segs_host.ctypes.data,
-                                     len(optimizer._segs_host), len(optimizer.param_groups) + 1, cs),
-                  "ps_table_check (offload pieces)")
+            check(lib.ps_piece_table_check(piece_rows.ctypes.data, len(piece_rows), len(optimizer._segs_host), cs),
+                  "ps_piece_table_check")
         desc = np.concatenate([base, np.array(rows, dtype=CHUNK_DESC_DTYPE)]) if rows else base
         optimizer._desc_host = desc
         optimizer._desc_dev = torch.from_numpy(desc.view(np.uint8).copy()).to(dev)

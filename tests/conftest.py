@@ -14,7 +14,8 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session", autouse=True)
 def _kernel_variant_from_env():
-    """PS_TEST_TUNE="bulk=1,unroll=1" runs the GPU tests on another kernel variant."""
+    """PS_TEST_TUNE="bulk=2,unroll=1" runs the GPU tests on another kernel variant
+    (keys and values as ps_tune takes them: bulk 0 / 2 / 3 / 4, unroll 1 / 2 / 4, ...)."""
     spec = os.environ.get("PS_TEST_TUNE", "")
     if spec:
         from patrickstar_b200 import _lib

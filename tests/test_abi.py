@@ -137,3 +137,23 @@ def test_table_check_looks_at_the_first_element_field(L):
     slots = (L.HyperSlot * 1)()
     rc = L.lib.ps_chunk_step_static(d.ctypes.data, 1, 8192, s.ctypes.data, 1, C.cast(slots, C.c_void_p), 1, 0, None)
     assert rc == L.PS_ERR_TABLE
+
+
+def test_piece_table_check(L):
+    """Host-only: descriptors of a piece [reserved, numel) of a chunk."""
+    d = np.zeros(2, dtype=L.CHUNK_DESC_DTYPE)
+    d["p32"], d["exp_avg"], d["exp_avg_sq"], d["h16"] = 256, 512, 768, 1024
+    d["numel"], d["reserved"] = [2048, 5000], [0, 4096]
+    d["seg_begin"], d["seg_end"] = 0, 3
+    chk = lambda: L.lib.ps_piece_table_check(d.ctypes.data, 2, 3, 8192)
+    assert chk() == 0
+    d["reserved"][1] = 4100
+    assert chk() == L.PS_ERR_TABLE
+    d["reserved"][1] = 6144
+    assert chk() == L.PS_ERR_TABLE      # at or beyond numel
+    d["reserved"][1] = 4096
+    d["seg_end"][0] = 4
+    assert chk() == L.PS_ERR_TABLE      # segment range outside the table
+    d["seg_end"][0] = 3
+    d["exp_avg"][1] = 520
+    assert chk() == L.PS_ERR_ALIGN

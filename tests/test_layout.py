@@ -176,3 +176,24 @@ def test_large_gpt_layouts_and_ownership(name, chunks, per_rank_at_8):
     # 12 B of fp32 state per parameter on the owner: the 40B model needs the offload tier under a 40 GB budget
     state_gib = per_rank_at_8 * 12 * cs / 2 ** 30
     assert (state_gib > 40) == (name == "gpt_40b")
+
+
+def test_handoff_counts_per_communication_group():
+    """Elements a tensor adds to each communication group's hand-off count (the trigger of the
+    group's reduce-scatter): tensors straddling chunks and groups are split at the boundaries,
+    and the per-group totals equal the elements in use in the group's chunks."""
+    cs, w = 100, 2
+    lay = ChunkLayout(cs, w, "flat")
+    lay.append_tensor_list([("a", 150, 0), ("b", 120, 1), ("c", 260, 0), ("d", 30, 1)])
+    lay.freeze()
+    assert lay.n_data_chunks == 6 and lay.n_groups_comm == 3
+    total = {}
+    per_tensor = {t.name: lay.add_to_comm_groups(t, {}) for t in lay.tensors}
+    for t in lay.tensors:
+        lay.add_to_comm_groups(t, total)
+    assert per_tensor["a"] == {0: 150}
+    assert per_tensor["b"] == {0: 50, 1: 70}
+    assert per_tensor["c"] == {1: 130, 2: 130}
+    assert per_tensor["d"] == {2: 30}
+    used = {g: sum(lay.chunk_numel(c) for c in range(g * w, (g + 1) * w)) for g in range(3)}
+    assert total == used == {0: 200, 1: 200, 2: 160}
