@@ -47,6 +47,8 @@ struct Tuning {
     int staged_blocks_per_sm = 1;  // ... and of the step kernel that runs beside it
     int p2p_unroll = 0;    // 0 = chosen from the world size
     int p2p_blocks_per_sm = 0;
+    int fused_min_blocks = 2;  // resident CTAs per SM the fused kernels' register budget is cut for
+    int p2p_min_blocks = 2;
 };
 Tuning g_tune;
 
@@ -765,8 +767,8 @@ __device__ __forceinline__ uint4 fused_prefetch(const ps_chunk_desc* chunks, uin
     return g;
 }
 
-template <int kFusedDepth>
-__global__ void __launch_bounds__(kThreads)
+template <int kFusedDepth, int kMinBlocks>
+__global__ void __launch_bounds__(kThreads, kMinBlocks)
 chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
                         uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
                         const ps_step_ctrl* __restrict__ ctrl, McCtx mc)
@@ -809,8 +811,8 @@ chunk_step_fused_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chu
 // Peer-to-peer form of the fused kernel (no multicast object needed; the sums are
 // exact fp32 accumulations).  Enough independent peer loads are in flight per
 // thread (W per 8-element group) that no register ring is needed.
-template <int U, int kColl>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int U, int kColl, int kMinBlocks>
+__global__ void __launch_bounds__(kThreads, kMinBlocks)
 chunk_step_p2p_kernel(const ps_chunk_desc* __restrict__ chunks, uint32_t n_chunks,
                       uint32_t tiles_per_chunk, const ps_segment* __restrict__ segs,
                       const ps_step_ctrl* __restrict__ ctrl, McCtx mc)
@@ -1478,7 +1480,7 @@ int launch_chunk_step_bulk(const ps_chunk_desc* chunks, uint32_t n_chunks, uint3
     return after_launch();
 }
 
-template <int kDepth>
+template <int kDepth, int kMinBlocks>
 int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
                             const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
 {
@@ -1488,14 +1490,14 @@ int launch_chunk_step_fused(const ps_chunk_desc* chunks, uint32_t n_chunks, uint
     int grid = 1;
     const int saved = g_tune.blocks_per_sm;
     g_tune.blocks_per_sm = g_tune.fused_blocks_per_sm;
-    int rc = grid_for(chunk_step_fused_kernel<kDepth>, total, &grid, 1);
+    int rc = grid_for(chunk_step_fused_kernel<kDepth, kMinBlocks>, total, &grid, 1);
     g_tune.blocks_per_sm = saved;
     if (rc != PS_OK) return rc;
-    chunk_step_fused_kernel<kDepth><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    chunk_step_fused_kernel<kDepth, kMinBlocks><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
     return after_launch();
 }
 
-template <int U, int kColl>
+template <int U, int kColl, int kMinBlocks = 2>
 int launch_chunk_step_p2p(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_t max_numel,
                           const ps_segment* segs, const ps_step_ctrl* ctrl, McCtx mc, cudaStream_t st)
 {
@@ -1504,10 +1506,10 @@ int launch_chunk_step_p2p(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32
     int grid = 1;
     const int saved = g_tune.blocks_per_sm;
     g_tune.blocks_per_sm = g_tune.p2p_blocks_per_sm;
-    int rc = grid_for(chunk_step_p2p_kernel<U, kColl>, (uint64_t)tpc * n_chunks, &grid, 2);
+    int rc = grid_for(chunk_step_p2p_kernel<U, kColl, kMinBlocks>, (uint64_t)tpc * n_chunks, &grid, 2);
     g_tune.blocks_per_sm = saved;
     if (rc != PS_OK) return rc;
-    chunk_step_p2p_kernel<U, kColl><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
+    chunk_step_p2p_kernel<U, kColl, kMinBlocks><<<grid, kThreads, 0, st>>>(chunks, n_chunks, tpc, segs, ctrl, mc);
     return after_launch();
 }
 
@@ -1659,6 +1661,12 @@ int ps_tune(const char* key, int value)
     } else if (!strcmp(key, "p2p_blocks_per_sm")) {
         if (value < 0 || value > 32) return PS_ERR_INVALID;
         g_tune.p2p_blocks_per_sm = value;
+    } else if (!strcmp(key, "fused_min_blocks")) {
+        if (value < 2 || value > 4) return PS_ERR_INVALID;
+        g_tune.fused_min_blocks = value;
+    } else if (!strcmp(key, "p2p_min_blocks")) {
+        if (value < 2 || value > 4) return PS_ERR_INVALID;
+        g_tune.p2p_min_blocks = value;
     } else if (!strcmp(key, "p2p_unroll")) {
         if (value != 0 && value != 1 && value != 2) return PS_ERR_INVALID;
         g_tune.p2p_unroll = value;
@@ -1981,10 +1989,16 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
     cudaStream_t st = (cudaStream_t)stream;
-    switch (g_tune.fused_depth) {
-        case 2: return launch_chunk_step_fused<2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-        case 8: return launch_chunk_step_fused<8>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-        default: return launch_chunk_step_fused<4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    // (reduced loads in flight per thread) x (resident CTAs per SM the register budget is cut for)
+    switch (g_tune.fused_depth * 10 + g_tune.fused_min_blocks) {
+        case 22: return launch_chunk_step_fused<2, 2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 23: return launch_chunk_step_fused<2, 3>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 24: return launch_chunk_step_fused<2, 4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 43: return launch_chunk_step_fused<4, 3>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 44: return launch_chunk_step_fused<4, 4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        case 82: case 83: case 84:
+            return launch_chunk_step_fused<8, 2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+        default: return launch_chunk_step_fused<4, 2>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
     }
 }
 
@@ -2142,10 +2156,16 @@ int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32
     cudaStream_t st = (cudaStream_t)stream;
     // few ranks: few peer loads per group, so two groups per thread keep the link busy
     int rc;
-    if (world_size <= 2 && g_tune.p2p_unroll == 1)
-        rc = launch_chunk_step_p2p<1, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
-    else if (world_size <= 2)
+    if (world_size <= 2 && g_tune.p2p_unroll == 2)
         rc = launch_chunk_step_p2p<2, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 2 && g_tune.p2p_min_blocks == 3)
+        rc = launch_chunk_step_p2p<1, 22, 3>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 2 && g_tune.p2p_min_blocks == 4)
+        rc = launch_chunk_step_p2p<1, 22, 4>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 2)   // one group per thread measured 10 % faster than two at 2 ranks
+        rc = launch_chunk_step_p2p<1, 22>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
+    else if (world_size <= 4 && g_tune.p2p_min_blocks == 3)
+        rc = launch_chunk_step_p2p<1, 24, 3>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
     else if (world_size <= 4)
         rc = launch_chunk_step_p2p<1, 24>(chunks_dev, n_chunks, max_numel, segs_dev, ctrl_dev, mc, st);
     else
