@@ -747,18 +747,18 @@ def run_e2e(args, w, steps):
     pinned memory N times over, so one pinned communication group's worth is fed to every group."""
     import torch
     client, opt, world, dev, cs, npr = w.client, w.opt, w.world, w.dev, w.cs, w.npr
-    host_out = torch.empty(npr * cs, dtype=torch.float16).pin_memory()
+    host_out = torch.empty(npr * cs, dtype=torch.float16, pin_memory=True)
     outs = [host_out[k * cs:(k + 1) * cs] for k in range(npr)]
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
     if world == 1:
-        host_in = torch.empty(npr * cs, dtype=torch.float16).pin_memory()
+        host_in = torch.empty(npr * cs, dtype=torch.float16, pin_memory=True)
         for k in range(npr):
             host_in[k * cs:(k + 1) * cs].copy_(w.pristine.roll(k * 4099))   # a distinct chunk each
         ins = [host_in[k * cs:(k + 1) * cs] for k in range(npr)]
         in_note = "%d distinct pinned gradient chunks" % npr
     else:
-        host_in = torch.empty(world * cs, dtype=torch.float16).pin_memory()
+        host_in = torch.empty(world * cs, dtype=torch.float16, pin_memory=True)
         host_in.copy_(w.pristine)
         in_note = "one pinned communication group of gradients (%d chunks) fed to each of the %d groups" % (world, w.n_groups)
 

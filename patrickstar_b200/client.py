@@ -149,7 +149,8 @@ class ChunkClient:
             return torch.zeros(max(self.n_resident, 0) * cs, dtype=torch.float32, device=dev)
 
         def host_buf():
-            return torch.zeros(n_off * cs, dtype=torch.float32).pin_memory() if n_off else None
+            # allocated pinned at once (no pageable copy first): tens of GiB per rank at scale
+            return torch.zeros(n_off * cs, dtype=torch.float32, pin_memory=True) if n_off else None
 
         self.p32, self.exp_avg, self.exp_avg_sq = dev_buf(), dev_buf(), dev_buf()
         self.p32_host, self.exp_avg_host, self.exp_avg_sq_host = host_buf(), host_buf(), host_buf()
@@ -220,7 +221,7 @@ class ChunkClient:
             d_old, h_old = getattr(self, name), getattr(self, name + "_host")
             d_new = torch.empty(new * cs, dtype=torch.float32, device=dev)
             n_off = n_local - new
-            h_new = torch.empty(n_off * cs, dtype=torch.float32).pin_memory() if n_off else None
+            h_new = torch.empty(n_off * cs, dtype=torch.float32, pin_memory=True) if n_off else None
             keep = min(old, new)
             d_new[:keep * cs].copy_(d_old[:keep * cs])
             if new > old:    # chunks old..new-1 come up from the host
