@@ -68,11 +68,12 @@ def parse_args():
     ap.add_argument("--scan", default="local", choices=["local", "reduced"],
                     help="N > 1: overflow test on local gradients before the reduction (the reference's "
                          "rule) or on the reduced ones")
-    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "fused", "p2p", "staged"],
+    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "fused", "p2p", "staged", "copy"],
                     help="N > 1: 'nccl' = NCCL reduce-scatter / all-gather pipelined around the step kernel; "
                          "'fused' = one kernel over NVSwitch multicast memory (multimem); 'p2p' = one kernel "
                          "over peer loads / stores; 'staged' = multimem puller + step kernel pipelined per "
-                         "chunk; 'auto' = p2p for 2-3 ranks, fused for more, nccl if symmetric memory cannot "
+                         "chunk; 'copy' = copy engines pull gradients / push params around a local step "
+                         "kernel, pipelined per chunk; 'auto' = p2p for 2-3 ranks, fused for more, nccl if symmetric memory cannot "
                          "be set up")
     ap.add_argument("--layout", default="uniform", choices=["uniform", "gpt2_1.5b", "gpt_12b", "gpt_40b"],
                     help="the headline workload's chunk list: 'uniform' = one tensor per chunk, --chunks per "
@@ -335,7 +336,7 @@ def workload_config(args, world, w=None):
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
-TRANSPORT_OF = {"fused": "multimem", "p2p": "p2p", "staged": "staged"}
+TRANSPORT_OF = {"fused": "multimem", "p2p": "p2p", "staged": "staged", "copy": "copy"}
 LAYOUT_MODELS = ("gpt2_1.5b", "gpt_12b", "gpt_40b")
 
 
@@ -566,7 +567,8 @@ def nvlink_roofline(w, timing):
     phases = timing.get("phase_ms")
     ms = phases["fused_kernel"] if phases else timing["total_ms"] / timing["steps"]
     kernel = {"fused": "chunk_step_fused_kernel", "p2p": "chunk_step_p2p_kernel",
-              "staged": "fused_pull_kernel + chunk_step_staged_kernel"}.get(w.collectives, "ncclDevKernel (reduce-scatter / all-gather)")
+              "staged": "fused_pull_kernel + chunk_step_staged_kernel",
+              "copy": "copy engines + chunk_step_p2p_kernel (local sums)"}.get(w.collectives, "ncclDevKernel (reduce-scatter / all-gather)")
     achieved = link_bytes / (ms * 1e-3) / 1e9
     out = {"bound": "nvlink", "kernel": kernel, "achieved": achieved, "peak": NVLINK_PEAK_GBS, "unit": "GB/s",
            "frac": achieved / NVLINK_PEAK_GBS,
@@ -635,7 +637,7 @@ def parity_leg(client, opt, scaler, collectives, hyper, adamw, followed, poison_
         torch.cuda.synchronize()
         dist.barrier()
         if transport is not None:
-            reduced = opt.reduced_gradients("p2p" if transport == "p2p" else "multimem", only=followed)
+            reduced = opt.reduced_gradients("p2p" if transport in ("p2p", "copy") else "multimem", only=followed)
             torch.cuda.synchronize()
             dist.barrier()
         else:
@@ -1120,6 +1122,7 @@ def run_ours(args):
             line["config"]["collectives"] = {
                 "fused": "fused into the step kernel (multimem ld_reduce / st over NVSwitch)",
                 "staged": "multimem ld_reduce puller + step kernel with multimem st, pipelined per chunk",
+                "copy": "copy engines pull gradients and push params around a local step kernel, pipelined per chunk",
                 "p2p": "fused into the step kernel (peer loads / stores over NVLink)"}.get(
                     collectives_used, line["config"]["collectives"])
             line["scaling_target_note"] = (

@@ -341,6 +341,33 @@ int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint
                                const uint64_t* peer_bases_dev, int world_size, uint16_t* staging_dev,
                                void* stream);
 
+#define PS_COPY_MAX_CHUNKS 4096u /* owned chunks per ps_chunk_step_copy call */
+
+/* The same multi-GPU step with the NVLink traffic handed to the copy engines,
+ * pipelined chunk by chunk over plain peer mappings: while the step kernel works
+ * on owned chunk k, the copy engines pull every peer's gradients of chunk k+1
+ * into local staging buffers (the reduce-scatter's traffic) and push the updated
+ * fp16 params of chunk k-1 into every peer's buffer (the all-gather's).  The
+ * kernel sums the own slot and the staged copies in rank order in fp32 and
+ * rounds once, exactly as ps_chunk_step_p2p does, so the two give identical
+ * bits; it touches local memory only.  NVLink bytes per direction, rank and
+ * group: 2 * (world_size - 1) chunks, at the copy engines' rate.
+ *   chunks_host       : host copy of the chunk table (the copies need the fp16
+ *                       addresses on the host)
+ *   peer_bases_host   : every rank's fp16 buffer base as mapped on this rank
+ *                       (world_size entries, entry `rank` = fp16_local_base)
+ *   staging_dev       : 2 * (world_size - 1) * max_numel fp16 elements (rounded
+ *                       up to a multiple of 8 per chunk copy), plain device memory
+ *   gather_table_dev  : n_chunks * world_size uint64 of device scratch
+ * ps_copy_pipe_create makes the streams and events (no device memory).  Same
+ * barriers across ranks as ps_chunk_step_fused; world_size <= 8. */
+int ps_copy_pipe_create(void** pipe_out);
+int ps_copy_pipe_destroy(void* pipe);
+int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chunk_desc* chunks_host,
+                       uint32_t n_chunks, uint32_t max_numel, const ps_segment* segs_dev,
+                       const ps_step_ctrl* ctrl_dev, const void* fp16_local_base, const uint64_t* peer_bases_host,
+                       int rank, int world_size, uint16_t* staging_dev, uint64_t* gather_table_dev, void* stream);
+
 /* dst[i] = the reduced gradient ps_chunk_step_p2p loads for the element at
  * fp16_local_ptr + 2*i of this rank's buffer.  For tests. */
 int ps_p2p_reduce_probe(const void* fp16_local_ptr, const void* fp16_local_base, const uint64_t* peer_bases_dev,

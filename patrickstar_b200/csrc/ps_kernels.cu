@@ -279,9 +279,18 @@ __device__ __forceinline__ void peers_st_f16(uint16_t* local_elem, uint32_t h, c
 // updated param is stored into every rank's buffer.
 constexpr int kMaxPeers = 8;
 // kColl values of the step templates: 0 no collective, 1 multimem, 2 / 24 / 22
-// peer-to-peer compiled for up to 8 / 4 / 2 ranks (fewer ranks, fewer registers)
-__host__ __device__ constexpr int peers_of(int kColl) { return kColl == 22 ? 2 : (kColl == 24 ? 4 : 8); }
-__host__ __device__ constexpr bool is_p2p(int kColl) { return kColl == 2 || kColl == 22 || kColl == 24; }
+// peer-to-peer compiled for up to 8 / 4 / 2 ranks (fewer ranks, fewer registers),
+// 38 / 34 / 32 the same summation over copies that the copy engines have brought
+// into local staging buffers, with the params stored locally only
+__host__ __device__ constexpr int peers_of(int kColl)
+{
+    return (kColl == 22 || kColl == 32) ? 2 : ((kColl == 24 || kColl == 34) ? 4 : 8);
+}
+__host__ __device__ constexpr bool is_staged_copies(int kColl) { return kColl == 32 || kColl == 34 || kColl == 38; }
+__host__ __device__ constexpr bool is_p2p(int kColl)
+{
+    return kColl == 2 || kColl == 22 || kColl == 24 || is_staged_copies(kColl);
+}
 
 template <int NP>
 __device__ __forceinline__ uint4 p2p_ld_reduce_f16x8(const uint16_t* local_vec, const McCtx& mc)
@@ -372,7 +381,7 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         if (i < sv.start || i >= sv.end) continue;
         float p = d.p32[i];
         if (kRestore) {
-            if (kColl)
+            if (kColl && !is_staged_copies(kColl))
                 peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
             else if (p16_out)
                 p16_out[i] = (uint16_t)float_to_half_bits(p);
@@ -393,7 +402,7 @@ __device__ __noinline__ void slow_group(const ps_chunk_desc d, const void* grads
         d.p32[i] = p;
         d.exp_avg[i] = m;
         d.exp_avg_sq[i] = v;
-        if (kColl)
+        if (kColl && !is_staged_copies(kColl))
             peers_st_f16(p16_out + i, float_to_half_bits(p), mc);
         else if (p16_out)
             p16_out[i] = (uint16_t)float_to_half_bits(p);
@@ -483,7 +492,7 @@ __device__ __forceinline__ void step_tile(const ps_chunk_desc& d, const ps_segme
         out.w = float_to_half_bits(p[6]) | (float_to_half_bits(p[7]) << 16);
         if (kColl == 1)
             mm_st_f16x8(reinterpret_cast<char*>(d.h16 + e[j]) + mc.mc_delta, out);
-        else if (is_p2p(kColl))
+        else if (is_p2p(kColl) && !is_staged_copies(kColl))
             p2p_st_f16x8<peers_of(kColl)>(d.h16 + e[j], out, mc);
         else
             st_stream(reinterpret_cast<uint4*>(d.h16 + e[j]), out);
@@ -1526,6 +1535,15 @@ int launch_chunk_restore(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_
     return after_launch();
 }
 
+// Streams and events of ps_chunk_step_copy (two staging slots, one pull and one push stream
+// per peer so that the copies to and from different peers run on different copy engines).
+struct CopyPipe {
+    int device = -1;
+    cudaStream_t pull[kMaxPeers] = {}, push[kMaxPeers] = {};
+    cudaEvent_t start = nullptr, stepped[2] = {nullptr, nullptr};
+    cudaEvent_t pulled[2][kMaxPeers] = {}, pushed[kMaxPeers] = {};
+};
+
 // Stream and events of ps_chunk_step_fused_staged (two staging slots).
 struct FusedPipe {
     int device = -1;
@@ -2084,6 +2102,163 @@ int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint
         rc = after_launch();
         if (rc != PS_OK) return rc;
         PS_CUDA(cudaEventRecord(p->freed[s], st));
+    }
+    return PS_OK;
+}
+
+int ps_copy_pipe_create(void** pipe_out)
+{
+    if (pipe_out == nullptr) return PS_ERR_INVALID;
+    auto* p = new CopyPipe();
+    bool ok = cudaGetDevice(&p->device) == cudaSuccess;
+    auto ev = [&](cudaEvent_t* e) { ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess; };
+    ev(&p->start);
+    ev(&p->stepped[0]);
+    ev(&p->stepped[1]);
+    for (int q = 0; q < kMaxPeers; ++q) {
+        ok = ok && cudaStreamCreateWithFlags(&p->pull[q], cudaStreamNonBlocking) == cudaSuccess;
+        ok = ok && cudaStreamCreateWithFlags(&p->push[q], cudaStreamNonBlocking) == cudaSuccess;
+        ev(&p->pulled[0][q]);
+        ev(&p->pulled[1][q]);
+        ev(&p->pushed[q]);
+    }
+    if (!ok) {
+        g_last_cuda_error = (int)cudaGetLastError();
+        ps_copy_pipe_destroy(p);
+        return PS_ERR_CUDA;
+    }
+    *pipe_out = p;
+    return PS_OK;
+}
+
+int ps_copy_pipe_destroy(void* pipe)
+{
+    if (pipe == nullptr) return PS_ERR_INVALID;
+    auto* p = static_cast<CopyPipe*>(pipe);
+    auto ev = [](cudaEvent_t e) { if (e) cudaEventDestroy(e); };
+    ev(p->start);
+    ev(p->stepped[0]);
+    ev(p->stepped[1]);
+    for (int q = 0; q < kMaxPeers; ++q) {
+        ev(p->pulled[0][q]);
+        ev(p->pulled[1][q]);
+        ev(p->pushed[q]);
+        if (p->pull[q]) cudaStreamDestroy(p->pull[q]);
+        if (p->push[q]) cudaStreamDestroy(p->push[q]);
+    }
+    delete p;
+    return PS_OK;
+}
+
+int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chunk_desc* chunks_host,
+                       uint32_t n_chunks, uint32_t max_numel, const ps_segment* segs_dev,
+                       const ps_step_ctrl* ctrl_dev, const void* fp16_local_base, const uint64_t* peer_bases_host,
+                       int rank, int world_size, uint16_t* staging_dev, uint64_t* gather_table_dev, void* stream)
+{
+    if (n_chunks == 0 || max_numel == 0) return PS_OK;
+    if (pipe == nullptr || chunks_dev == nullptr || chunks_host == nullptr || segs_dev == nullptr ||
+        ctrl_dev == nullptr || fp16_local_base == nullptr || peer_bases_host == nullptr ||
+        staging_dev == nullptr || gather_table_dev == nullptr)
+        return PS_ERR_INVALID;
+    if (world_size < 2 || world_size > kMaxPeers) return PS_ERR_LIMIT;
+    if (rank < 0 || rank >= world_size) return PS_ERR_INVALID;
+    if (n_chunks > PS_COPY_MAX_CHUNKS) return PS_ERR_LIMIT;
+    if (((uintptr_t)fp16_local_base | (uintptr_t)staging_dev) & 15u) return PS_ERR_ALIGN;
+    if (max_numel >= 0x7fffff00u) return PS_ERR_LIMIT;
+    if (peer_bases_host[rank] != (uint64_t)(uintptr_t)fp16_local_base) return PS_ERR_INVALID;
+    auto* p = static_cast<CopyPipe*>(pipe);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int W = world_size;
+    const size_t slot_elems = ((size_t)max_numel + kVec - 1) / kVec * kVec;  // one peer's copy of one chunk
+    auto staging_of = [&](int s, int peer_index) {
+        return staging_dev + ((size_t)s * (W - 1) + peer_index) * slot_elems;
+    };
+    // Per chunk, per rank: the address at which the step kernel finds that rank's gradients
+    // of the chunk, minus the chunk's byte offset in the fp16 buffer (the kernel adds the
+    // offset of the element it works on): the own slot itself, or the staging copy.
+    static thread_local std::unique_ptr<uint64_t[]> table;
+    if (!table) table.reset(new (std::nothrow) uint64_t[(size_t)PS_COPY_MAX_CHUNKS * kMaxPeers]);
+    if (!table) return PS_ERR_INVALID;
+    for (uint32_t k = 0; k < n_chunks; ++k) {
+        const uint64_t off = (uint64_t)((const char*)chunks_host[k].h16 - (const char*)fp16_local_base);
+        if (((uintptr_t)chunks_host[k].h16 & 15u) != 0) return PS_ERR_ALIGN;
+        int pi = 0;
+        for (int r = 0; r < W; ++r) {
+            if (r == rank)
+                table[(size_t)k * W + r] = (uint64_t)(uintptr_t)fp16_local_base;
+            else
+                table[(size_t)k * W + r] = (uint64_t)(uintptr_t)staging_of((int)(k & 1u), pi++) - off;
+        }
+    }
+    PS_CUDA(cudaMemcpyAsync(gather_table_dev, table.get(), (size_t)n_chunks * W * sizeof(uint64_t),
+                            cudaMemcpyHostToDevice, st));
+    PS_CUDA(cudaEventRecord(p->start, st));
+    for (int q = 0; q < W - 1; ++q) {
+        PS_CUDA(cudaStreamWaitEvent(p->pull[q], p->start, 0));
+        PS_CUDA(cudaStreamWaitEvent(p->push[q], p->start, 0));
+    }
+    DeviceInfo di;
+    int rc = device_info(&di);
+    if (rc != PS_OK) return rc;
+    constexpr int U = 2;
+    constexpr uint32_t kTile = kThreads * kVec * U;
+    for (uint32_t k = 0; k < n_chunks; ++k) {
+        const int s = (int)(k & 1u);
+        const ps_chunk_desc& d = chunks_host[k];
+        const size_t off = (size_t)((const char*)d.h16 - (const char*)fp16_local_base);
+        const size_t bytes = ((size_t)d.numel * 2 + 15) / 16 * 16;
+        // 1. the copy engines pull every peer's gradients of this chunk into the slot's staging
+        int pi = 0;
+        for (int r = 0; r < W; ++r) {
+            if (r == rank) continue;
+            if (k >= 2) PS_CUDA(cudaStreamWaitEvent(p->pull[pi], p->stepped[s], 0));  // slot free again
+            if (bytes)
+                PS_CUDA(cudaMemcpyAsync(staging_of(s, pi), (const char*)(uintptr_t)peer_bases_host[r] + off, bytes,
+                                        cudaMemcpyDeviceToDevice, p->pull[pi]));
+            PS_CUDA(cudaEventRecord(p->pulled[s][pi], p->pull[pi]));
+            PS_CUDA(cudaStreamWaitEvent(st, p->pulled[s][pi], 0));
+            ++pi;
+        }
+        // 2. sum in rank order, step, fp16 params into the own slot
+        if (d.numel) {
+            McCtx mc;
+            mc.mc_delta = 0;
+            mc.peers = reinterpret_cast<const unsigned long long*>(gather_table_dev + (size_t)k * W);
+            mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
+            mc.world = W;
+            const uint32_t tpc = (uint32_t)(((uint64_t)d.numel + kTile - 1) / kTile);
+            int grid = 1;
+            if (W <= 2) {
+                rc = grid_for(chunk_step_p2p_kernel<U, 32, 2>, tpc, &grid, 2);
+                if (rc != PS_OK) return rc;
+                chunk_step_p2p_kernel<U, 32, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc, segs_dev, ctrl_dev, mc);
+            } else if (W <= 4) {
+                rc = grid_for(chunk_step_p2p_kernel<U, 34, 2>, tpc, &grid, 2);
+                if (rc != PS_OK) return rc;
+                chunk_step_p2p_kernel<U, 34, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc, segs_dev, ctrl_dev, mc);
+            } else {
+                rc = grid_for(chunk_step_p2p_kernel<1, 38, 2>, tpc * 2, &grid, 2);
+                if (rc != PS_OK) return rc;
+                chunk_step_p2p_kernel<1, 38, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc * 2, segs_dev, ctrl_dev, mc);
+            }
+            rc = after_launch();
+            if (rc != PS_OK) return rc;
+        }
+        PS_CUDA(cudaEventRecord(p->stepped[s], st));
+        // 3. the copy engines push the updated fp16 params into every peer's buffer
+        pi = 0;
+        for (int r = 0; r < W; ++r) {
+            if (r == rank) continue;
+            PS_CUDA(cudaStreamWaitEvent(p->push[pi], p->stepped[s], 0));
+            if (bytes)
+                PS_CUDA(cudaMemcpyAsync((char*)(uintptr_t)peer_bases_host[r] + off, (const char*)fp16_local_base + off,
+                                        bytes, cudaMemcpyDeviceToDevice, p->push[pi]));
+            ++pi;
+        }
+    }
+    for (int q = 0; q < W - 1; ++q) {
+        PS_CUDA(cudaEventRecord(p->pushed[q], p->push[q]));
+        PS_CUDA(cudaStreamWaitEvent(st, p->pushed[q], 0));
     }
     return PS_OK;
 }

@@ -551,7 +551,10 @@ class FP16Adam(torch.optim.Optimizer):
         the links for 2-3 ranks, dearer for 8);
         ``transport="staged"``: the multimem form as a two-kernel pipeline — a light
         puller brings chunk k+1's reduced gradients into a local staging buffer
-        while the step kernel updates chunk k (same results bit for bit).
+        while the step kernel updates chunk k (same results bit for bit);
+        ``transport="copy"``: the copy engines pull the peers' gradients of chunk
+        k+1 and push the params of chunk k-1 while a purely local kernel updates
+        chunk k (same bits as "p2p"; the links run at the copy engines' rate).
 
         ``scan="done"``: the gradients were tested when they were handed over
         (``handoff_grad``), so the scan of the whole fp16 buffer is left out."""
@@ -596,8 +599,23 @@ class FP16Adam(torch.optim.Optimizer):
                                                      c.fp16_multicast_ptr, c.peer_bases.data_ptr(),
                                                      c.world_size, self._fused_staging.data_ptr(), st),
                       "ps_chunk_step_fused_staged")
+            elif transport == "copy":
+                if getattr(self, "_copy_pipe", None) is None:
+                    self._copy_pipe = C.c_void_p()
+                    check(lib.ps_copy_pipe_create(C.byref(self._copy_pipe)), "ps_copy_pipe_create")
+                    slot = (self._max_numel_resident + 7) // 8 * 8
+                    self._copy_staging = torch.empty(2 * (c.world_size - 1) * slot, dtype=torch.float16,
+                                                     device=self.device)
+                    self._copy_table = torch.empty(max(c.n_resident, 1) * c.world_size, dtype=torch.int64,
+                                                   device=self.device)
+                    self._peer_bases_host = (C.c_uint64 * c.world_size)(*[int(p) for p in c.symm_handle.buffer_ptrs])
+                check(lib.ps_chunk_step_copy(self._copy_pipe, self._desc_dev.data_ptr(), self._desc_host.ctypes.data,
+                                             c.n_resident, self._max_numel_resident, self._segs_dev.data_ptr(),
+                                             self._ctrl.data_ptr(), c.fp16.data_ptr(), self._peer_bases_host,
+                                             c.rank, c.world_size, self._copy_staging.data_ptr(),
+                                             self._copy_table.data_ptr(), st), "ps_chunk_step_copy")
             else:
-                raise ValueError("transport must be 'multimem', 'p2p' or 'staged'")
+                raise ValueError("transport must be 'multimem', 'p2p', 'staged' or 'copy'")
             self._update_torch_params(st)
             mark("kernel")
             if getattr(self, "_barrier_buf", None) is None:
@@ -634,6 +652,10 @@ class FP16Adam(torch.optim.Optimizer):
         if pipe is not None and pipe.value:
             lib.ps_fused_pipe_destroy(pipe)
             self._fused_pipe = None
+        pipe = getattr(self, "_copy_pipe", None)
+        if pipe is not None and pipe.value:
+            lib.ps_copy_pipe_destroy(pipe)
+            self._copy_pipe = None
 
     # --------------------------------------------------------------- inspection
     def read_ctrl(self) -> StepCtrl:
