@@ -68,7 +68,7 @@ def parse_args():
     ap.add_argument("--scan", default="local", choices=["local", "reduced"],
                     help="N > 1: overflow test on local gradients before the reduction (the reference's "
                          "rule) or on the reduced ones")
-    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "fused", "p2p", "staged", "copy"],
+    ap.add_argument("--collectives", default="auto", choices=["auto", "nccl", "fused", "p2p", "staged", "copy", "copy_pull"],
                     help="N > 1: 'nccl' = NCCL reduce-scatter / all-gather pipelined around the step kernel; "
                          "'fused' = one kernel over NVSwitch multicast memory (multimem); 'p2p' = one kernel "
                          "over peer loads / stores; 'staged' = multimem puller + step kernel pipelined per "
@@ -97,6 +97,10 @@ def parse_args():
                          "gradient hand-off) followed by the step, with each communication group's "
                          "reduce-scatter fired from the hand-off and with all of them issued at step(); prints "
                          "that report instead of the headline line")
+    ap.add_argument("--rs-max-ctas", type=int, default=0,
+                    help="--handoff-overlap: cap on the CTAs of the reduce-scatter communicator (0 = NCCL's default)")
+    ap.add_argument("--backward", default="matmul", choices=["matmul", "elementwise"],
+                    help="--handoff-overlap: the stand-in for a parameter's backward compute")
     ap.add_argument("--offload-slots", type=int, default=2)
     ap.add_argument("--offload-piece", type=int, default=16 * 1024 * 1024, help="elements per staged piece")
     return ap.parse_args()
@@ -336,7 +340,7 @@ def workload_config(args, world, w=None):
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
-TRANSPORT_OF = {"fused": "multimem", "p2p": "p2p", "staged": "staged", "copy": "copy"}
+TRANSPORT_OF = {"fused": "multimem", "p2p": "p2p", "staged": "staged", "copy": "copy", "copy_pull": "copy_pull"}
 LAYOUT_MODELS = ("gpt2_1.5b", "gpt_12b", "gpt_40b")
 
 
@@ -354,7 +358,7 @@ class Workload:
     """One chunk list on this rank with its optimizer, gradients source and step function."""
 
     def __init__(self, args, layout, world, rank, local_rank, dev, collectives, npr=None, cs=None,
-                 budget=None, seed=1000):
+                 budget=None, seed=1000, rs_max_ctas=None):
         import numpy as np
         import torch
         from patrickstar_b200 import ChunkClient, DynamicLossScaler, FP16Adam
@@ -368,7 +372,7 @@ class Workload:
 
         def make_client(symmetric):
             c = ChunkClient(rank=local_rank, default_chunk_size=cs, world_size=world, device=dev, pack="flat",
-                            symmetric=symmetric)
+                            symmetric=symmetric, rs_max_ctas=rs_max_ctas)
             if layout in LAYOUT_MODELS:
                 from patrickstar_b200.model_layouts import model_specs
                 c.append_tensor_list([(n, int(np.prod(sh)), g) for n, sh, g in model_specs(layout)])
@@ -568,7 +572,8 @@ def nvlink_roofline(w, timing):
     ms = phases["fused_kernel"] if phases else timing["total_ms"] / timing["steps"]
     kernel = {"fused": "chunk_step_fused_kernel", "p2p": "chunk_step_p2p_kernel",
               "staged": "fused_pull_kernel + chunk_step_staged_kernel",
-              "copy": "copy engines + chunk_step_p2p_kernel (local sums)"}.get(w.collectives, "ncclDevKernel (reduce-scatter / all-gather)")
+              "copy": "copy engines + chunk_step_p2p_kernel (local sums)",
+              "copy_pull": "copy engines (pull) + chunk_step_p2p_kernel (local sums, peer stores)"}.get(w.collectives, "ncclDevKernel (reduce-scatter / all-gather)")
     achieved = link_bytes / (ms * 1e-3) / 1e9
     out = {"bound": "nvlink", "kernel": kernel, "achieved": achieved, "peak": NVLINK_PEAK_GBS, "unit": "GB/s",
            "frac": achieved / NVLINK_PEAK_GBS,
@@ -578,7 +583,8 @@ def nvlink_roofline(w, timing):
            "bytes_formula": "%d chunks of fp16 per direction, rank and communication group (%s) x %d groups"
                             % (chunks, "world + 1: in-switch reduction and multicast store" if w.collectives in
                                ("fused", "staged") else "2 * (world - 1): peer or ring exchange", w.n_groups),
-           "launch_ms": ms, "timed_over": "the fused kernel alone (CUDA events)" if phases else "the whole step",
+           "launch_ms": ms, "timed_over": (("the copy / step pipeline alone" if w.collectives == "copy" else
+                                            "the fused kernel alone") + " (CUDA events)") if phases else "the whole step",
            "launches_timed": timing["steps"]}
     if phases:
         step_ms = timing["total_ms"] / timing["steps"]
@@ -637,7 +643,7 @@ def parity_leg(client, opt, scaler, collectives, hyper, adamw, followed, poison_
         torch.cuda.synchronize()
         dist.barrier()
         if transport is not None:
-            reduced = opt.reduced_gradients("p2p" if transport in ("p2p", "copy") else "multimem", only=followed)
+            reduced = opt.reduced_gradients("p2p" if transport in ("p2p", "copy", "copy_pull") else "multimem", only=followed)
             torch.cuda.synchronize()
             dist.barrier()
         else:
@@ -856,6 +862,24 @@ def agree(w_or_world, dev, ok):
     return bool(t.item())
 
 
+def build_agreed(world, dev, *a, **kw):
+    """A Workload built on every rank, or None on every rank: a rank that cannot build it (out of
+    device or pinned memory) must not leave the others waiting in the workload's first
+    collective, so the ranks agree on the outcome before any of them goes on."""
+    import torch
+    w, why = None, None
+    try:
+        w = Workload(*a, **kw)
+    except (RuntimeError, MemoryError) as e:
+        why = "%s: %s" % (type(e).__name__, str(e).splitlines()[0][:200] if str(e) else "")
+    if agree(world, dev, w is not None):
+        return w, None
+    if w is not None:
+        w.free()
+    torch.cuda.empty_cache()
+    return None, why or "another rank could not build the workload"
+
+
 def run_config2(args, world, rank, local_rank, dev):
     """GPT-2 1.5B layout on one GPU: what the segment tables cost beside the uniform workload."""
     w = Workload(args, "gpt2_1.5b", 1, 0, local_rank, dev, "none")
@@ -883,7 +907,9 @@ def run_config3(args, world, rank, local_rank, dev, collectives):
     need = (n_chunks or 192) * (2 * cs + 12 * cs // world) + (4 << 30)
     if not agree(world, dev, free > need):
         return {"omitted": "not enough free device memory: %.1f GiB free, %.1f GiB needed" % (free / 2 ** 30, need / 2 ** 30)}
-    w = Workload(args, "gpt_12b", world, rank, local_rank, dev, collectives, seed=3000)
+    w, why = build_agreed(world, dev, args, "gpt_12b", world, rank, local_rank, dev, collectives, seed=3000)
+    if w is None:
+        return {"omitted": "the workload could not be built on every rank (%s)" % why}
     parity = workload_parity_leg(w)
     steps = 20
     t = w.time_steps(steps, args.warmup)
@@ -924,7 +950,10 @@ def run_config4(args, world, rank, local_rank, dev):
     if not agree(world, dev, host_ok and free > dev_need):
         return {"omitted": "not enough memory on this box: %.0f GiB of pinned host memory and %.0f GiB per GPU needed"
                            % (pinned_need * world / 2 ** 30, dev_need / 2 ** 30)}
-    w = Workload(args, args.config4_layout, world, rank, local_rank, dev, "nccl", budget=budget, seed=4000)
+    w, why = build_agreed(world, dev, args, args.config4_layout, world, rank, local_rank, dev, "nccl",
+                          budget=budget, seed=4000)
+    if w is None:
+        return {"omitted": "the workload could not be built on every rank (%s)" % why}
     assert w.client.n_resident == n_res, (w.client.n_resident, n_res)
     parity = workload_parity_leg(w)
     steps = 3
@@ -1269,18 +1298,26 @@ def run_handoff_overlap(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
-    w = Workload(args, "uniform", world, rank, local_rank, dev, "nccl", npr=args.chunks)
+    w = Workload(args, "uniform", world, rank, local_rank, dev, "nccl", npr=args.chunks,
+                 rs_max_ctas=args.rs_max_ctas or None)
     client, opt, cs = w.client, w.opt, w.cs
     params = list(client.params.values())[::-1]
     grad_src = w.pristine[:cs]
     a = torch.randn(8192, 8192, dtype=torch.bfloat16, device=dev)
     c = torch.empty_like(a)
+    x = torch.randn(3 * cs, dtype=torch.float32, device=dev)
+
+    def compute_one():
+        if args.backward == "matmul":
+            torch.matmul(a, a, out=c)        # compute-bound: ~0.8 ms on every SM
+        else:
+            x.mul_(1.0001)                   # memory-bound: 1.6 GB through HBM, ~0.27 ms
 
     def backward_and_step(trigger, compute=True):
         opt.rs_on_handoff = trigger
         for p in params:
             if compute:
-                torch.matmul(a, a, out=c)
+                compute_one()
             p.grad = grad_src.view(p.shape)
             opt.handoff_grad(p)
         opt.step_with_collectives(scan="done")
@@ -1305,7 +1342,7 @@ def run_handoff_overlap(args):
 
     def compute_only():
         for _ in params:
-            torch.matmul(a, a, out=c)
+            compute_one()
 
     def rs_only():
         for wk in [client.reduce_scatter_group(g, async_op=True) for g in range(w.n_groups)]:
@@ -1315,9 +1352,12 @@ def run_handoff_overlap(args):
     ctrl = opt.read_ctrl()
     if rank == 0:
         print(json.dumps({
-            "workload": "stand-in backward (one 8192^3 bf16 matmul per parameter, %d parameters = chunks of %d "
-                        "elements, last to first) + gradient hand-off + step with NCCL collectives, %d ranks"
-                        % (len(params), cs, world),
+            "workload": "stand-in backward (%s per parameter, %d parameters = chunks of %d "
+                        "elements, last to first) + gradient hand-off + step with NCCL collectives, %d ranks; "
+                        "reduce-scatter communicator: %s"
+                        % ("one 8192^3 bf16 matmul" if args.backward == "matmul" else "one 1.6 GB elementwise pass",
+                           len(params), cs, world,
+                           "max %d CTAs" % args.rs_max_ctas if args.rs_max_ctas else "NCCL's default CTAs"),
             "ms_reduce_scatter_issued_at_step": at_step, "ms_reduce_scatter_fired_from_handoff": from_handoff,
             "ms_backward_compute_alone": compute_ms, "ms_all_reduce_scatters_alone": rs_ms,
             "reduce_scatter_time_hidden_ms": at_step - from_handoff,

@@ -356,17 +356,23 @@ int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint
  *                       addresses on the host)
  *   peer_bases_host   : every rank's fp16 buffer base as mapped on this rank
  *                       (world_size entries, entry `rank` = fp16_local_base)
- *   staging_dev       : 2 * (world_size - 1) * max_numel fp16 elements (rounded
- *                       up to a multiple of 8 per chunk copy), plain device memory
+ *   peer_bases_dev    : NULL, or the same array in device memory: the kernel then
+ *                       stores the fp16 params into every rank's buffer itself
+ *                       (posted peer stores) and the copy engines only pull
+ *   staging_dev       : n_slots * (world_size - 1) * max_numel fp16 elements
+ *                       (rounded up to a multiple of 8 per chunk copy), plain
+ *                       device memory; more slots let the pulls run further ahead
  *   gather_table_dev  : n_chunks * world_size uint64 of device scratch
- * ps_copy_pipe_create makes the streams and events (no device memory).  Same
- * barriers across ranks as ps_chunk_step_fused; world_size <= 8. */
-int ps_copy_pipe_create(void** pipe_out);
+ * ps_copy_pipe_create makes the streams and events for n_slots (2..8) staging
+ * slots (no device memory).  Same barriers across ranks as ps_chunk_step_fused;
+ * world_size <= 8. */
+int ps_copy_pipe_create(void** pipe_out, int n_slots);
 int ps_copy_pipe_destroy(void* pipe);
 int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chunk_desc* chunks_host,
                        uint32_t n_chunks, uint32_t max_numel, const ps_segment* segs_dev,
                        const ps_step_ctrl* ctrl_dev, const void* fp16_local_base, const uint64_t* peer_bases_host,
-                       int rank, int world_size, uint16_t* staging_dev, uint64_t* gather_table_dev, void* stream);
+                       const uint64_t* peer_bases_dev, int rank, int world_size, uint16_t* staging_dev,
+                       uint64_t* gather_table_dev, void* stream);
 
 /* dst[i] = the reduced gradient ps_chunk_step_p2p loads for the element at
  * fp16_local_ptr + 2*i of this rank's buffer.  For tests. */

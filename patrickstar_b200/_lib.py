@@ -122,9 +122,9 @@ SIGNATURES = {
     "ps_fused_pipe_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "ps_fused_pipe_destroy": (C.c_int, [_p]),
     "ps_chunk_step_fused_staged": (C.c_int, [_p, _p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, _p, C.c_int, _p, _p]),
-    "ps_copy_pipe_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "ps_copy_pipe_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
     "ps_copy_pipe_destroy": (C.c_int, [_p]),
-    "ps_chunk_step_copy": (C.c_int, [_p, _p, _p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, C.c_int, C.c_int, _p, _p, _p]),
+    "ps_chunk_step_copy": (C.c_int, [_p, _p, _p, C.c_uint32, C.c_uint32, _p, _p, _p, _p, _p, C.c_int, C.c_int, _p, _p, _p]),
     "ps_restore_fp16": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p]),
     "ps_tensor_table_step": (C.c_int, [_p, C.c_uint32, C.c_uint32, _p, _p, _p]),
     "ps_p2p_reduce_probe": (C.c_int, [_p, _p, _p, C.c_int, _p, C.c_size_t, _p]),

@@ -29,7 +29,7 @@ from .chunk_list import ChunkLayout, DEFAULT_CHUNK_SIZE
 
 class ChunkClient:
     def __init__(self, rank=0, default_chunk_size=DEFAULT_CHUNK_SIZE, config=None, world_size=None,
-                 device=None, pack="no_split", process_group=None, symmetric=False):
+                 device=None, pack="no_split", process_group=None, symmetric=False, rs_max_ctas=None):
         if not torch.cuda.is_available():
             raise RuntimeError("patrickstar_b200 needs a CUDA device (sm_100a); none found")
         self.local_rank = rank
@@ -52,7 +52,13 @@ class ChunkClient:
         if world_size > 1 and torch.distributed.is_initialized():
             ranks = torch.distributed.get_process_group_ranks(
                 process_group if process_group is not None else torch.distributed.group.WORLD)
-            self.pg_reduce_scatter = torch.distributed.new_group(ranks)
+            rs_options = None
+            if rs_max_ctas:
+                # a reduce-scatter fired from the backward hand-off runs beside backward's
+                # compute kernels: capping its CTAs leaves them the SMs
+                rs_options = torch.distributed.ProcessGroupNCCL.Options()
+                rs_options.config.max_ctas = int(rs_max_ctas)
+            self.pg_reduce_scatter = torch.distributed.new_group(ranks, pg_options=rs_options)
             self.pg_all_gather = torch.distributed.new_group(ranks)
         self.device = torch.device("cuda", rank) if device is None else torch.device(device)
         self.config = config or {}

@@ -251,7 +251,9 @@ __device__ __forceinline__ void mm_st_f16x8(void* mc, uint4 v)
 // plain peer stores.
 struct McCtx {
     long long mc_delta;                 // multicast mapping minus local fp16 buffer, in bytes
-    const unsigned long long* peers;    // every rank's fp16 buffer base (device array)
+    const unsigned long long* peers;    // every rank's fp16 buffer base (device array): where params are stored
+    const unsigned long long* gather;   // per rank, where its gradients are read from: the same bases
+                                        // (peer loads), or local staging copies biased by the chunk's offset
     const char* local_base;             // this rank's fp16 buffer base
     int world;
 };
@@ -299,7 +301,7 @@ __device__ __forceinline__ uint4 p2p_ld_reduce_f16x8(const uint16_t* local_vec, 
     uint4 q[NP];
 #pragma unroll
     for (int r = 0; r < NP; ++r)
-        if (r < mc.world) q[r] = *reinterpret_cast<const uint4*>(mc.peers[r] + off);
+        if (r < mc.world) q[r] = *reinterpret_cast<const uint4*>(mc.gather[r] + off);
     float acc[8];
     uint32_t w0[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
 #pragma unroll
@@ -324,9 +326,9 @@ __device__ __forceinline__ uint4 p2p_ld_reduce_f16x8(const uint16_t* local_vec, 
 __device__ __forceinline__ uint32_t p2p_ld_reduce_f16(const uint16_t* local_elem, const McCtx& mc)
 {
     const long long off = reinterpret_cast<const char*>(local_elem) - mc.local_base;
-    float acc = half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.peers[0] + off));
+    float acc = half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.gather[0] + off));
     for (int r = 1; r < mc.world; ++r)
-        acc = __fadd_rn(acc, half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.peers[r] + off)));
+        acc = __fadd_rn(acc, half_bits_to_float(*reinterpret_cast<const uint16_t*>(mc.gather[r] + off)));
     return float_to_half_bits(acc);
 }
 template <int NP>
@@ -1004,6 +1006,7 @@ multimem_reduce_probe_kernel(const uint16_t* mc, uint16_t* dst, size_t n)
             McCtx ctx;
             ctx.mc_delta = 0;  // `mc` already is the multicast address
             ctx.peers = nullptr;
+            ctx.gather = nullptr;
             ctx.local_base = nullptr;
             ctx.world = 0;
             dst[i] = (uint16_t)mm_ld_reduce_f16(mc + i, ctx);
@@ -1537,11 +1540,13 @@ int launch_chunk_restore(const ps_chunk_desc* chunks, uint32_t n_chunks, uint32_
 
 // Streams and events of ps_chunk_step_copy (two staging slots, one pull and one push stream
 // per peer so that the copies to and from different peers run on different copy engines).
+constexpr int kCopyMaxSlots = 8;
 struct CopyPipe {
     int device = -1;
+    int n_slots = 2;
     cudaStream_t pull[kMaxPeers] = {}, push[kMaxPeers] = {};
-    cudaEvent_t start = nullptr, stepped[2] = {nullptr, nullptr};
-    cudaEvent_t pulled[2][kMaxPeers] = {}, pushed[kMaxPeers] = {};
+    cudaEvent_t start = nullptr, stepped[kCopyMaxSlots] = {};
+    cudaEvent_t pulled[kCopyMaxSlots][kMaxPeers] = {}, pushed[kMaxPeers] = {};
 };
 
 // Stream and events of ps_chunk_step_fused_staged (two staging slots).
@@ -2004,6 +2009,7 @@ int ps_chunk_step_fused(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint
     McCtx mc;
     mc.mc_delta = (long long)((intptr_t)fp16_multicast_base - (intptr_t)fp16_local_base);
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.gather = mc.peers;
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
     cudaStream_t st = (cudaStream_t)stream;
@@ -2073,6 +2079,7 @@ int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint
     McCtx mc;
     mc.mc_delta = (long long)((intptr_t)fp16_multicast_base - (intptr_t)fp16_local_base);
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.gather = mc.peers;
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
     DeviceInfo di;
@@ -2106,20 +2113,20 @@ int ps_chunk_step_fused_staged(void* pipe, const ps_chunk_desc* chunks_dev, uint
     return PS_OK;
 }
 
-int ps_copy_pipe_create(void** pipe_out)
+int ps_copy_pipe_create(void** pipe_out, int n_slots)
 {
     if (pipe_out == nullptr) return PS_ERR_INVALID;
+    if (n_slots < 2 || n_slots > kCopyMaxSlots) return PS_ERR_INVALID;
     auto* p = new CopyPipe();
+    p->n_slots = n_slots;
     bool ok = cudaGetDevice(&p->device) == cudaSuccess;
     auto ev = [&](cudaEvent_t* e) { ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess; };
     ev(&p->start);
-    ev(&p->stepped[0]);
-    ev(&p->stepped[1]);
+    for (int s = 0; s < n_slots; ++s) ev(&p->stepped[s]);
     for (int q = 0; q < kMaxPeers; ++q) {
         ok = ok && cudaStreamCreateWithFlags(&p->pull[q], cudaStreamNonBlocking) == cudaSuccess;
         ok = ok && cudaStreamCreateWithFlags(&p->push[q], cudaStreamNonBlocking) == cudaSuccess;
-        ev(&p->pulled[0][q]);
-        ev(&p->pulled[1][q]);
+        for (int s = 0; s < n_slots; ++s) ev(&p->pulled[s][q]);
         ev(&p->pushed[q]);
     }
     if (!ok) {
@@ -2137,11 +2144,9 @@ int ps_copy_pipe_destroy(void* pipe)
     auto* p = static_cast<CopyPipe*>(pipe);
     auto ev = [](cudaEvent_t e) { if (e) cudaEventDestroy(e); };
     ev(p->start);
-    ev(p->stepped[0]);
-    ev(p->stepped[1]);
+    for (int s = 0; s < kCopyMaxSlots; ++s) ev(p->stepped[s]);
     for (int q = 0; q < kMaxPeers; ++q) {
-        ev(p->pulled[0][q]);
-        ev(p->pulled[1][q]);
+        for (int s = 0; s < kCopyMaxSlots; ++s) ev(p->pulled[s][q]);
         ev(p->pushed[q]);
         if (p->pull[q]) cudaStreamDestroy(p->pull[q]);
         if (p->push[q]) cudaStreamDestroy(p->push[q]);
@@ -2153,7 +2158,8 @@ int ps_copy_pipe_destroy(void* pipe)
 int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chunk_desc* chunks_host,
                        uint32_t n_chunks, uint32_t max_numel, const ps_segment* segs_dev,
                        const ps_step_ctrl* ctrl_dev, const void* fp16_local_base, const uint64_t* peer_bases_host,
-                       int rank, int world_size, uint16_t* staging_dev, uint64_t* gather_table_dev, void* stream)
+                       const uint64_t* peer_bases_dev, int rank, int world_size, uint16_t* staging_dev,
+                       uint64_t* gather_table_dev, void* stream)
 {
     if (n_chunks == 0 || max_numel == 0) return PS_OK;
     if (pipe == nullptr || chunks_dev == nullptr || chunks_host == nullptr || segs_dev == nullptr ||
@@ -2169,6 +2175,7 @@ int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chu
     auto* p = static_cast<CopyPipe*>(pipe);
     cudaStream_t st = (cudaStream_t)stream;
     const int W = world_size;
+    const uint32_t S = (uint32_t)p->n_slots;
     const size_t slot_elems = ((size_t)max_numel + kVec - 1) / kVec * kVec;  // one peer's copy of one chunk
     auto staging_of = [&](int s, int peer_index) {
         return staging_dev + ((size_t)s * (W - 1) + peer_index) * slot_elems;
@@ -2187,7 +2194,7 @@ int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chu
             if (r == rank)
                 table[(size_t)k * W + r] = (uint64_t)(uintptr_t)fp16_local_base;
             else
-                table[(size_t)k * W + r] = (uint64_t)(uintptr_t)staging_of((int)(k & 1u), pi++) - off;
+                table[(size_t)k * W + r] = (uint64_t)(uintptr_t)staging_of((int)(k % S), pi++) - off;
         }
     }
     PS_CUDA(cudaMemcpyAsync(gather_table_dev, table.get(), (size_t)n_chunks * W * sizeof(uint64_t),
@@ -2203,7 +2210,7 @@ int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chu
     constexpr int U = 2;
     constexpr uint32_t kTile = kThreads * kVec * U;
     for (uint32_t k = 0; k < n_chunks; ++k) {
-        const int s = (int)(k & 1u);
+        const int s = (int)(k % S);
         const ps_chunk_desc& d = chunks_host[k];
         const size_t off = (size_t)((const char*)d.h16 - (const char*)fp16_local_base);
         const size_t bytes = ((size_t)d.numel * 2 + 15) / 16 * 16;
@@ -2211,7 +2218,7 @@ int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chu
         int pi = 0;
         for (int r = 0; r < W; ++r) {
             if (r == rank) continue;
-            if (k >= 2) PS_CUDA(cudaStreamWaitEvent(p->pull[pi], p->stepped[s], 0));  // slot free again
+            if (k >= S) PS_CUDA(cudaStreamWaitEvent(p->pull[pi], p->stepped[s], 0));  // slot free again
             if (bytes)
                 PS_CUDA(cudaMemcpyAsync(staging_of(s, pi), (const char*)(uintptr_t)peer_bases_host[r] + off, bytes,
                                         cudaMemcpyDeviceToDevice, p->pull[pi]));
@@ -2223,31 +2230,35 @@ int ps_chunk_step_copy(void* pipe, const ps_chunk_desc* chunks_dev, const ps_chu
         if (d.numel) {
             McCtx mc;
             mc.mc_delta = 0;
-            mc.peers = reinterpret_cast<const unsigned long long*>(gather_table_dev + (size_t)k * W);
+            mc.gather = reinterpret_cast<const unsigned long long*>(gather_table_dev + (size_t)k * W);
+            mc.peers = peer_bases_dev ? reinterpret_cast<const unsigned long long*>(peer_bases_dev) : mc.gather;
             mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
             mc.world = W;
             const uint32_t tpc = (uint32_t)(((uint64_t)d.numel + kTile - 1) / kTile);
             int grid = 1;
-            if (W <= 2) {
-                rc = grid_for(chunk_step_p2p_kernel<U, 32, 2>, tpc, &grid, 2);
-                if (rc != PS_OK) return rc;
-                chunk_step_p2p_kernel<U, 32, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc, segs_dev, ctrl_dev, mc);
-            } else if (W <= 4) {
-                rc = grid_for(chunk_step_p2p_kernel<U, 34, 2>, tpc, &grid, 2);
-                if (rc != PS_OK) return rc;
-                chunk_step_p2p_kernel<U, 34, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc, segs_dev, ctrl_dev, mc);
-            } else {
-                rc = grid_for(chunk_step_p2p_kernel<1, 38, 2>, tpc * 2, &grid, 2);
-                if (rc != PS_OK) return rc;
-                chunk_step_p2p_kernel<1, 38, 2><<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tpc * 2, segs_dev, ctrl_dev, mc);
-            }
+            // params: pushed by the copy engines afterwards (the kernel stores locally only), or
+            // stored into every rank's buffer by the kernel itself when peer_bases_dev is given
+            auto launch = [&](auto kernel, uint32_t tiles) -> int {
+                int r2 = grid_for(kernel, tiles, &grid, 2);
+                if (r2 != PS_OK) return r2;
+                kernel<<<grid, kThreads, 0, st>>>(chunks_dev + k, 1, tiles, segs_dev, ctrl_dev, mc);
+                return PS_OK;
+            };
+            const bool kernel_stores = peer_bases_dev != nullptr;
+            if (W <= 2)
+                rc = kernel_stores ? launch(chunk_step_p2p_kernel<U, 22, 2>, tpc) : launch(chunk_step_p2p_kernel<U, 32, 2>, tpc);
+            else if (W <= 4)
+                rc = kernel_stores ? launch(chunk_step_p2p_kernel<U, 24, 2>, tpc) : launch(chunk_step_p2p_kernel<U, 34, 2>, tpc);
+            else
+                rc = kernel_stores ? launch(chunk_step_p2p_kernel<1, 2, 2>, tpc * 2) : launch(chunk_step_p2p_kernel<1, 38, 2>, tpc * 2);
+            if (rc != PS_OK) return rc;
             rc = after_launch();
             if (rc != PS_OK) return rc;
         }
         PS_CUDA(cudaEventRecord(p->stepped[s], st));
         // 3. the copy engines push the updated fp16 params into every peer's buffer
         pi = 0;
-        for (int r = 0; r < W; ++r) {
+        for (int r = 0; r < W && peer_bases_dev == nullptr; ++r) {
             if (r == rank) continue;
             PS_CUDA(cudaStreamWaitEvent(p->push[pi], p->stepped[s], 0));
             if (bytes)
@@ -2326,6 +2337,7 @@ int ps_chunk_step_p2p(const ps_chunk_desc* chunks_dev, uint32_t n_chunks, uint32
     McCtx mc;
     mc.mc_delta = 0;
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.gather = mc.peers;
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
     cudaStream_t st = (cudaStream_t)stream;
@@ -2359,6 +2371,7 @@ int ps_p2p_reduce_probe(const void* fp16_local_ptr, const void* fp16_local_base,
     McCtx mc;
     mc.mc_delta = 0;
     mc.peers = reinterpret_cast<const unsigned long long*>(peer_bases_dev);
+    mc.gather = mc.peers;
     mc.local_base = reinterpret_cast<const char*>(fp16_local_base);
     mc.world = world_size;
     DeviceInfo di;

@@ -554,7 +554,9 @@ class FP16Adam(torch.optim.Optimizer):
         while the step kernel updates chunk k (same results bit for bit);
         ``transport="copy"``: the copy engines pull the peers' gradients of chunk
         k+1 and push the params of chunk k-1 while a purely local kernel updates
-        chunk k (same bits as "p2p"; the links run at the copy engines' rate).
+        chunk k (same bits as "p2p"; the links run at the copy engines' rate);
+        ``transport="copy_pull"``: the copy engines only pull; the kernel stores the
+        params into every rank's buffer itself (posted peer stores).
 
         ``scan="done"``: the gradients were tested when they were handed over
         (``handoff_grad``), so the scan of the whole fp16 buffer is left out."""
@@ -599,12 +601,13 @@ class FP16Adam(torch.optim.Optimizer):
                                                      c.fp16_multicast_ptr, c.peer_bases.data_ptr(),
                                                      c.world_size, self._fused_staging.data_ptr(), st),
                       "ps_chunk_step_fused_staged")
-            elif transport == "copy":
+            elif transport in ("copy", "copy_pull"):
                 if getattr(self, "_copy_pipe", None) is None:
                     self._copy_pipe = C.c_void_p()
-                    check(lib.ps_copy_pipe_create(C.byref(self._copy_pipe)), "ps_copy_pipe_create")
+                    n_slots = int(getattr(self, "copy_slots", 4))
+                    check(lib.ps_copy_pipe_create(C.byref(self._copy_pipe), n_slots), "ps_copy_pipe_create")
                     slot = (self._max_numel_resident + 7) // 8 * 8
-                    self._copy_staging = torch.empty(2 * (c.world_size - 1) * slot, dtype=torch.float16,
+                    self._copy_staging = torch.empty(n_slots * (c.world_size - 1) * slot, dtype=torch.float16,
                                                      device=self.device)
                     self._copy_table = torch.empty(max(c.n_resident, 1) * c.world_size, dtype=torch.int64,
                                                    device=self.device)
@@ -612,10 +615,11 @@ class FP16Adam(torch.optim.Optimizer):
                 check(lib.ps_chunk_step_copy(self._copy_pipe, self._desc_dev.data_ptr(), self._desc_host.ctypes.data,
                                              c.n_resident, self._max_numel_resident, self._segs_dev.data_ptr(),
                                              self._ctrl.data_ptr(), c.fp16.data_ptr(), self._peer_bases_host,
+                                             c.peer_bases.data_ptr() if transport == "copy_pull" else None,
                                              c.rank, c.world_size, self._copy_staging.data_ptr(),
                                              self._copy_table.data_ptr(), st), "ps_chunk_step_copy")
             else:
-                raise ValueError("transport must be 'multimem', 'p2p', 'staged' or 'copy'")
+                raise ValueError("transport must be 'multimem', 'p2p', 'staged', 'copy' or 'copy_pull'")
             self._update_torch_params(st)
             mark("kernel")
             if getattr(self, "_barrier_buf", None) is None:

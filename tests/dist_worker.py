@@ -12,8 +12,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 SCAN = os.environ.get("PS_TEST_SCAN", "local")
-FUSED = ("fused", "p2p", "staged", "copy")  # the forms over symmetric memory
-TRANSPORT = {"fused": "multimem", "p2p": "p2p", "staged": "staged", "copy": "copy"}
+FUSED = ("fused", "p2p", "staged", "copy", "copy_pull")  # the forms over symmetric memory
+TRANSPORT = {"fused": "multimem", "p2p": "p2p", "staged": "staged", "copy": "copy", "copy_pull": "copy_pull"}
 
 
 def main():
@@ -71,7 +71,7 @@ def main():
         if SCAN in FUSED:
             # what the fused kernel's reduction returns for this rank's chunks
             dist.barrier()
-            reduced = opt.reduced_gradients("p2p" if SCAN in ("p2p", "copy") else "multimem")
+            reduced = opt.reduced_gradients("p2p" if SCAN in ("p2p", "copy", "copy_pull") else "multimem")
             torch.cuda.synchronize()
             dist.barrier()
         else:
@@ -93,7 +93,7 @@ def main():
                     # ulp of the exact sum, inside the (world - 1) / 2 ulp a ring of fp16
                     # additions may be off by for world >= 3
                     tol = 2.0 ** -10 * want.abs() + 2.0 ** -24
-                elif SCAN in ("p2p", "copy"):
+                elif SCAN in ("p2p", "copy", "copy_pull"):
                     # fp32 accumulation in rank order (each addition within 2^-24 relative of
                     # the partial sum), one rounding to fp16
                     tol = 2.0 ** -11 * want.abs() + world * 2.0 ** -23 * mag[c * cs:(c + 1) * cs] + 2.0 ** -25

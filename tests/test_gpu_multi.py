@@ -13,8 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 # every form at 2 ranks; at 4 and 8 ranks the forms the benchmark picks there plus one NCCL form
-COMBOS = [(2, "local"), (2, "reduced"), (2, "fused"), (2, "p2p"), (2, "staged"), (2, "copy"),
-          (4, "reduced"), (4, "fused"), (4, "p2p"), (4, "staged"), (4, "copy"),
+COMBOS = [(2, "local"), (2, "reduced"), (2, "fused"), (2, "p2p"), (2, "staged"), (2, "copy"), (2, "copy_pull"),
+          (4, "reduced"), (4, "fused"), (4, "p2p"), (4, "staged"), (4, "copy"), (4, "copy_pull"),
           (8, "local"), (8, "fused"), (8, "staged"), (8, "copy")]
 
 
