@@ -22,9 +22,10 @@ One key is added under the reference's ``client.opts`` block
 ``"nccl"``: NCCL reduce-scatter / all-gather pipelined around the step kernel,
 each group's reduce-scatter fired from the backward hand-off;
 ``"multimem"`` / ``"p2p"``: one kernel that does the reduction, the step and
-the gather over NVSwitch multicast memory or peer mappings; ``"auto"``
-(default): p2p for 2-3 ranks, multimem for more, nccl when symmetric memory
-cannot be set up.
+the gather over NVSwitch multicast memory or peer mappings; ``"staged"`` /
+``"copy"``: the pipelined two-kernel and copy-engine forms of the same exchange;
+``"auto"`` (default): p2p for 2-3 ranks, multimem for more, nccl when symmetric
+memory cannot be set up.
 """
 import torch
 
@@ -76,10 +77,14 @@ def parse_config(config):
     if "gradient_clipping" in config:
         out["gradient_clipping"] = config["gradient_clipping"]
     mode = ((config.get("client") or {}).get("opts") or {}).get("fused_collectives", "auto")
-    if mode not in ("auto", "nccl", "multimem", "p2p"):
-        raise ValueError("client.opts.fused_collectives must be auto, nccl, multimem or p2p; got %r" % (mode,))
+    if mode not in ("auto", "nccl", "multimem", "p2p", "staged", "copy"):
+        raise ValueError("client.opts.fused_collectives must be auto, nccl, multimem, p2p, staged or copy; "
+                         "got %r" % (mode,))
     out["fused_collectives"] = mode
     return out
+
+
+_SYMMETRIC_FORMS = ("multimem", "p2p", "staged", "copy")   # need the fp16 chunk list in symmetric memory
 
 
 def resolve_collectives(mode, world_size):
@@ -122,7 +127,7 @@ class ChunkStepEngine(torch.nn.Module):
         # how a data-parallel step exchanges chunks; the fused forms need the fp16 chunk list
         # in symmetric memory
         want = collectives or resolve_collectives(parsed["fused_collectives"], client.world_size)
-        if want in ("multimem", "p2p") and client.symm_handle is None:
+        if want in _SYMMETRIC_FORMS and client.symm_handle is None:
             want = "nccl"
         self.collectives = want
         # NCCL form: a group's reduce-scatter starts as soon as its gradients are complete
@@ -156,7 +161,7 @@ class ChunkStepEngine(torch.nn.Module):
         if self.client.world_size > 1:
             # data parallel: reduce-scatter of the gradient chunks, rank-local step,
             # all-gather of the param chunks (patrickstar/core/client.py:818-856, 428-497)
-            if self.collectives in ("multimem", "p2p"):
+            if self.collectives in _SYMMETRIC_FORMS:
                 return self.optimizer.step_fused_collectives(self.collectives, scan="done" if scanned else "local")
             return self.optimizer.step_with_collectives(scan="done" if scanned else "local")
         return self.optimizer.step(scan=not scanned)
@@ -170,7 +175,7 @@ def _client_for(parsed, local_rank, config):
     want = resolve_collectives(parsed["fused_collectives"], world)
     kw = dict(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
               config=(config or {}).get("client", None))
-    return ChunkClient(symmetric=want in ("multimem", "p2p"), **kw), want
+    return ChunkClient(symmetric=want in _SYMMETRIC_FORMS, **kw), want
 
 
 def initialize_engine(model_func, local_rank, config=None, client=None):

@@ -157,3 +157,28 @@ def test_piece_table_check(L):
     d["seg_end"][0] = 3
     d["exp_avg"][1] = 520
     assert chk() == L.PS_ERR_ALIGN
+
+
+def test_tuning_knobs_accept_only_their_values(L):
+    """ps_tune: every knob takes its documented values and refuses others."""
+    ok = {"unroll": (1, 2, 4), "scan_unroll": (1, 2, 4), "blocks_per_sm": (0, 2, 32), "bulk": (0, 2, 3, 4),
+          "fused_depth": (2, 4, 8), "fused_min_blocks": (2, 3, 4), "fused_blocks_per_sm": (0, 4),
+          "pull_blocks_per_sm": (1, 2), "staged_blocks_per_sm": (1, 2), "p2p_unroll": (0, 1, 2),
+          "p2p_min_blocks": (2, 3, 4), "p2p_blocks_per_sm": (0, 4)}
+    bad = {"unroll": (0, 3), "bulk": (1, 5), "fused_depth": (1, 3, 16), "fused_min_blocks": (1, 5), "p2p_unroll": (3,),
+           "blocks_per_sm": (-1, 33)}
+    defaults = {"unroll": 2, "scan_unroll": 4, "blocks_per_sm": 0, "bulk": 0, "fused_depth": 4, "fused_min_blocks": 2,
+                "fused_blocks_per_sm": 0, "pull_blocks_per_sm": 2, "staged_blocks_per_sm": 1, "p2p_unroll": 0,
+                "p2p_min_blocks": 2, "p2p_blocks_per_sm": 0}
+    try:
+        for key, values in ok.items():
+            for v in values:
+                assert L.lib.ps_tune(key.encode(), v) == 0, (key, v)
+        for key, values in bad.items():
+            for v in values:
+                assert L.lib.ps_tune(key.encode(), v) == L.PS_ERR_INVALID, (key, v)
+        assert L.lib.ps_tune(b"no_such_knob", 1) == L.PS_ERR_INVALID
+        assert L.lib.ps_tune(None, 1) == L.PS_ERR_INVALID
+    finally:
+        for key, v in defaults.items():
+            assert L.lib.ps_tune(key.encode(), v) == 0

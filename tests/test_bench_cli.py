@@ -29,3 +29,14 @@ def test_reference_arm_other_ranks_stay_silent():
                         "--chunks", "1", "--chunk-size", "4096", "--steps", "1", "--warmup", "0"],
                        capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_nvlink_byte_formula_is_the_documented_one():
+    """One formula for the NVLink bytes of a multi-GPU step: in-switch forms move world + 1 chunks
+    per direction, rank and group; peer, ring and copy-engine forms 2 * (world - 1)."""
+    import bench
+    for w in (2, 4, 8):
+        assert bench.nvlink_chunks_per_group("fused", w) == w + 1
+        assert bench.nvlink_chunks_per_group("staged", w) == w + 1
+        for form in ("p2p", "nccl", "copy", "copy_pull"):
+            assert bench.nvlink_chunks_per_group(form, w) == 2 * (w - 1)
