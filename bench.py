@@ -310,7 +310,7 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": workload_config(args, 1),
+        "config": workload_config(args, max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
                          "sample": "%d of %d chunks per step (overflow test + adam_update + fp16 cast), "
                                    "all host threads" % (sample, nchunks)},
@@ -917,6 +917,7 @@ def run_config3(args, world, rank, local_rank, dev, collectives):
     assert ctrl.n_skipped == 1, ctrl.n_skipped      # the parity leg's poisoned step only
     out = {"workload": w.describe(), "value": w.total_params * steps / (t["total_ms"] * 1e-3), "unit": UNIT,
            "ms_per_step": t["total_ms"] / steps, "steps": steps, "collectives": w.collectives,
+           "free_device_gib_before": free / 2 ** 30,
            "chunks_per_rank": w.npr, "roofline": nvlink_roofline(w, t), "multi_gpu_parity": parity}
     if w.note:
         out["note"] = w.note
@@ -989,6 +990,7 @@ def run_config4(args, world, rank, local_rank, dev):
     n_off = len(off)
     out = {"workload": w.describe(), "value": w.total_params * steps / (t["total_ms"] * 1e-3), "unit": UNIT,
            "ms_per_step": step_ms, "steps": steps, "state_budget_bytes_per_gpu": budget,
+           "free_device_gib_before": free / 2 ** 30,
            "chunks_per_rank": w.npr, "resident_per_rank": client.n_resident, "offloaded_per_rank": n_off,
            "pinned_host_bytes_all_ranks": pinned_need * world,
            "h2d_ms_alone": h2d_ms, "d2h_ms_alone": d2h_ms,
@@ -1147,13 +1149,17 @@ def run_ours(args):
         if local_step is not None:
             line["local_step"] = local_step
             line["step_with_scan_done_at_handoff"] = scan_done
-            line["config"]["overflow_scan"] = "local" if fused else args.scan
-            line["config"]["collectives"] = {
-                "fused": "fused into the step kernel (multimem ld_reduce / st over NVSwitch)",
-                "staged": "multimem ld_reduce puller + step kernel with multimem st, pipelined per chunk",
-                "copy": "copy engines pull gradients and push params around a local step kernel, pipelined per chunk",
-                "p2p": "fused into the step kernel (peer loads / stores over NVLink)"}.get(
-                    collectives_used, line["config"]["collectives"])
+            # how the exchange named in `config` is carried out (kept out of `config`, which names the
+            # workload and is the same for the CPU reference arm)
+            line["transport"] = {
+                "overflow_scan": "local" if fused else args.scan,
+                "collectives": {
+                    "fused": "fused into the step kernel (multimem ld_reduce / st over NVSwitch)",
+                    "staged": "multimem ld_reduce puller + step kernel with multimem st, pipelined per chunk",
+                    "copy": "copy engines pull gradients and push params around a local step kernel, pipelined per chunk",
+                    "copy_pull": "copy engines pull gradients; the step kernel stores params to every rank",
+                    "p2p": "fused into the step kernel (peer loads / stores over NVLink)"}.get(
+                        collectives_used, "NCCL reduce-scatter / all-gather pipelined around the step kernel")}
             line["scaling_target_note"] = (
                 "the >= 7x at 8 GPUs target is met by local_step (rank-local part); `value` includes the "
                 "reduce-scatter and all-gather, whose NVLink bytes bound it at about 1.3x a single GPU")
