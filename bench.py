@@ -947,7 +947,8 @@ def run_config4(args, world, rank, local_rank, dev):
     dev_need = (per_rank * world) * 2 * cs + n_res * 12 * cs + (6 << 30)
     host_ok = True
     if rank == 0:
-        host_ok = host_memory_available() > pinned_need * world + (16 << 30)
+        # every rank's process also holds a few GiB of host memory of its own (CUDA context, torch)
+        host_ok = host_memory_available() > pinned_need * world + (6 << 30) * world + (16 << 30)
     if not agree(world, dev, host_ok and free > dev_need):
         return {"omitted": "not enough memory on this box: %.0f GiB of pinned host memory and %.0f GiB per GPU needed"
                            % (pinned_need * world / 2 ** 30, dev_need / 2 ** 30)}

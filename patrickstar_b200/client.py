@@ -67,7 +67,8 @@ class ChunkClient:
         self.params = {}      # name -> fp16 nn.Parameter view
         self.fp16 = None
         self.p32 = self.exp_avg = self.exp_avg_sq = None          # device-resident local chunks
-        self.p32_host = self.exp_avg_host = self.exp_avg_sq_host = None  # offloaded local chunks
+        # offloaded local chunks: one pinned host tensor per chunk and kind (None when there are none)
+        self.p32_host = self.exp_avg_host = self.exp_avg_sq_host = None
         self.n_resident = 0
         self.local_ids = []
         self._pending = []    # (name, nn.Parameter) registered from a module, placed at allocate()
@@ -155,8 +156,7 @@ class ChunkClient:
             return torch.zeros(max(self.n_resident, 0) * cs, dtype=torch.float32, device=dev)
 
         def host_buf():
-            # allocated pinned at once (no pageable copy first): tens of GiB per rank at scale
-            return torch.zeros(n_off * cs, dtype=torch.float32, pin_memory=True) if n_off else None
+            return self._pinned_chunks(n_off, zero=True)
 
         self.p32, self.exp_avg, self.exp_avg_sq = dev_buf(), dev_buf(), dev_buf()
         self.p32_host, self.exp_avg_host, self.exp_avg_sq_host = host_buf(), host_buf(), host_buf()
@@ -179,6 +179,16 @@ class ChunkClient:
         for name, (p, _) in self.torch_params.items():
             p.data = p.data.to(device=dev, dtype=torch.float32)
         return self
+
+    def _pinned_chunks(self, n, zero=False):
+        """``n`` chunk-sized fp32 buffers in pinned host memory, or None for n = 0.
+        One allocation per chunk, made pinned at once: torch's pinned-memory
+        allocator rounds every request up to a power of two, which for one buffer
+        of tens of GiB per rank would waste up to as much again."""
+        if n <= 0:
+            return None
+        make = torch.zeros if zero else torch.empty
+        return [make(self.layout.chunk_size, dtype=torch.float32, pin_memory=True) for _ in range(n)]
 
     def _derive_n_resident(self, budget, reserve=0, held=0):
         """How many local chunks keep their fp32 state in HBM.  ``None``: all;
@@ -214,7 +224,6 @@ class ChunkClient:
         if budget is None:
             return False
         cs = self.layout.chunk_size
-        n_local = len(self.local_ids)
         old = self.n_resident
         new = self._derive_n_resident(budget, held=3 * 4 * cs * old)
         self._budget = budget
@@ -224,23 +233,22 @@ class ChunkClient:
         torch.cuda.current_stream(dev).synchronize()   # no step may be in flight on the states
         names = ("p32", "exp_avg", "exp_avg_sq")
         for name in names:   # one kind at a time: the transient extra HBM is one third of the state
-            d_old, h_old = getattr(self, name), getattr(self, name + "_host")
+            d_old, h_old = getattr(self, name), getattr(self, name + "_host") or []
             d_new = torch.empty(new * cs, dtype=torch.float32, device=dev)
-            n_off = n_local - new
-            h_new = torch.empty(n_off * cs, dtype=torch.float32, pin_memory=True) if n_off else None
             keep = min(old, new)
             d_new[:keep * cs].copy_(d_old[:keep * cs])
             if new > old:    # chunks old..new-1 come up from the host
-                d_new[old * cs:new * cs].copy_(h_old[:(new - old) * cs])
-                if n_off:
-                    h_new.copy_(h_old[(new - old) * cs:])
+                for i in range(new - old):
+                    d_new[(old + i) * cs:(old + i + 1) * cs].copy_(h_old[i])
+                h_new = h_old[new - old:]
             else:            # chunks new..old-1 go down to the host
-                h_new[:(old - new) * cs].copy_(d_old[new * cs:old * cs])
-                if h_old is not None:
-                    h_new[(old - new) * cs:].copy_(h_old)
+                h_new = self._pinned_chunks(old - new)
+                for i in range(old - new):
+                    h_new[i].copy_(d_old[(new + i) * cs:(new + i + 1) * cs])
+                h_new = h_new + list(h_old)
             torch.cuda.current_stream(dev).synchronize()
             setattr(self, name, d_new)
-            setattr(self, name + "_host", h_new)
+            setattr(self, name + "_host", h_new or None)
             del d_old, h_old
         self.n_resident = new
         return True
@@ -266,8 +274,7 @@ class ChunkClient:
             sl = slice(local_index * cs, (local_index + 1) * cs)
             return self.p32[sl], self.exp_avg[sl], self.exp_avg_sq[sl]
         k = local_index - self.n_resident
-        sl = slice(k * cs, (k + 1) * cs)
-        return self.p32_host[sl], self.exp_avg_host[sl], self.exp_avg_sq_host[sl]
+        return self.p32_host[k], self.exp_avg_host[k], self.exp_avg_sq_host[k]
 
     def is_local(self, name):
         """True when every element of the tensor lies in chunks this rank owns."""
