@@ -487,10 +487,12 @@ int ps_chunk_step_static(const ps_chunk_desc* chunks_host, uint32_t n_chunks, ui
  * per tile of the step kernels), "scan_unroll" (1, 2, 4), "blocks_per_sm"
  * (0 = occupancy calculator), "bulk" (0, or 2..4 stages of the bulk-async
  * staged chunk step), "fused_depth" (2, 4, 8: reduced-gradient loads a thread
- * of ps_chunk_step_fused keeps in flight), "fused_blocks_per_sm",
- * "pull_blocks_per_sm" / "staged_blocks_per_sm" (grids of the two kernels of
- * ps_chunk_step_fused_staged), "p2p_unroll" (0 = by world size, 1, 2),
- * "p2p_blocks_per_sm".  No counterpart in the reference. */
+ * of ps_chunk_step_fused keeps in flight), "fused_min_blocks" / "p2p_min_blocks"
+ * (2..4: resident CTAs per SM the fused kernels' register budget is cut for),
+ * "fused_blocks_per_sm", "pull_blocks_per_sm" / "staged_blocks_per_sm" (grids of
+ * the two kernels of ps_chunk_step_fused_staged), "p2p_unroll" (0 = by world
+ * size, 1, 2), "p2p_blocks_per_sm".  The defaults are the measured best; no
+ * counterpart in the reference. */
 int ps_tune(const char* key, int value);
 
 /* Kernel launch counter: number of kernels this library has launched in this
