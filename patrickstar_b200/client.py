@@ -70,6 +70,7 @@ class ChunkClient:
         # offloaded local chunks: one pinned host tensor per chunk and kind (None when there are none)
         self.p32_host = self.exp_avg_host = self.exp_avg_sq_host = None
         self.n_resident = 0
+        self._budget = None   # what allocate() was given: None, bytes, or "auto"
         self.local_ids = []
         self._pending = []    # (name, nn.Parameter) registered from a module, placed at allocate()
         # parameters managed by torch instead of the chunk list (the reference's TORCH_BASED
@@ -208,8 +209,15 @@ class ChunkClient:
             return max(0, min(n_local, int((free - reserve + held) * ratio) // per_chunk))
         return max(0, min(n_local, int(budget) // per_chunk))
 
-    # replaced by tests to play a device that is short of memory
-    mem_get_info = staticmethod(torch.cuda.mem_get_info)
+    @staticmethod
+    def mem_get_info(device):
+        """(bytes this process can still place on the device, total bytes): what the
+        driver reports free plus what torch's caching allocator holds but is not
+        using (it hands that out again before asking the driver).  Replaced by
+        tests to play a device that is short of memory."""
+        free, total = torch.cuda.mem_get_info(device)
+        cached = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+        return free + max(0, cached), total
 
     def rebalance(self, state_budget_bytes=None):
         """Re-derive the hybrid placement from the memory that is free NOW and move

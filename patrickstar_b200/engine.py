@@ -158,10 +158,16 @@ class ChunkStepEngine(torch.nn.Module):
         """optimizer.step() without a second overflow scan when every gradient came
         through ``backward`` above."""
         scanned, self._grads_scanned = getattr(self, "_grads_scanned", False), False
+        if self.client._budget == "auto":
+            # hybrid placement follows the memory that is free now, step by step
+            # (patrickstar/ops/fp16_cpu_adam.py:523-528); moves nothing while the split holds
+            self.optimizer.rebalance()
         if self.client.world_size > 1:
             # data parallel: reduce-scatter of the gradient chunks, rank-local step,
             # all-gather of the param chunks (patrickstar/core/client.py:818-856, 428-497)
-            if self.collectives in _SYMMETRIC_FORMS:
+            # (chunks whose state lives in pinned host memory go through the offload pipeline,
+            # which the NCCL form drives; it works on symmetric memory as well)
+            if self.collectives in _SYMMETRIC_FORMS and self.optimizer._offload is None:
                 return self.optimizer.step_fused_collectives(self.collectives, scan="done" if scanned else "local")
             return self.optimizer.step_with_collectives(scan="done" if scanned else "local")
         return self.optimizer.step(scan=not scanned)
@@ -191,8 +197,11 @@ def initialize_engine(model_func, local_rank, config=None, client=None):
         model = model_func()
         model.to(dtype=torch.float16)
         client.register_module(model)
+        # use_hybrid_adam (the reference's default): as many chunk states in HBM as the memory
+        # left over allows, the rest in pinned host memory, re-decided every step
+        budget = "auto" if parsed["optim_params"].get("use_hybrid_adam", True) else None
         try:
-            client.allocate()
+            client.allocate(state_budget_bytes=budget)
             ok = 1
         except RuntimeError:
             if not client.symmetric:
@@ -206,7 +215,7 @@ def initialize_engine(model_func, local_rank, config=None, client=None):
                 client = ChunkClient(rank=local_rank, default_chunk_size=parsed["default_chunk_size"],
                                      config=(config or {}).get("client", None))
                 client.register_module(model)
-                client.allocate()
+                client.allocate(state_budget_bytes=budget)
                 collectives = "nccl"
     engine = ChunkStepEngine(model=model, client=client, config=config, collectives=collectives)
     return (engine, engine.optimizer)

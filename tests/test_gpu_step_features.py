@@ -265,3 +265,50 @@ def test_scale_loss_runs_on_the_device_state():
     assert torch.equal(w.grad, 2 * w.detach() * 512)
     half_loss = (w.half() * 2).sum()
     assert sc.scale_loss(half_loss).dtype == torch.float16
+
+
+def test_engine_follows_free_memory_step_by_step():
+    """initialize_engine with use_hybrid_adam (the default) places chunk states by the memory
+    that is free and re-decides before every step (fp16_cpu_adam.py:523-528).  Two identical
+    engines train on the same batch; one of them is told, through a faked ``mem_get_info``,
+    that memory runs short from iteration 3 on and recovers at iteration 7.  Its chunk states
+    move to pinned host memory and back, and every parameter stays bit-identical to the
+    undisturbed engine's."""
+    from patrickstar_b200 import initialize_engine
+
+    def model_func():
+        torch.manual_seed(3)
+        return torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.Tanh(), torch.nn.Linear(40, 40),
+                                   torch.nn.Tanh(), torch.nn.Linear(40, 40), torch.nn.Tanh(),
+                                   torch.nn.Linear(40, 8))
+
+    cfg = {"optimizer": {"type": "AdamW", "params": {"lr": 1e-3, "eps": 1e-6, "weight_decay": 0.01}},
+           "fp16": {"enabled": True, "loss_scale": 0, "initial_scale_power": 8, "loss_scale_window": 1000,
+                    "hysteresis": 2, "min_loss_scale": 1},
+           "default_chunk_size": 2048, "client": {"mem_tracer": {"margin_use_ratio": 1.0}}}
+    a, _ = initialize_engine(model_func, 0, cfg)
+    b, _ = initialize_engine(model_func, 0, cfg)
+    n_local = len(b.client.local_ids)
+    assert n_local >= 3 and a.client._budget == "auto" and a.client.n_resident == b.client.n_resident == n_local
+    per_chunk = 12 * 2048
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(16, 24, device=DEV, dtype=torch.float16, generator=gen)
+    y = torch.randn(16, 8, device=DEV, generator=gen)
+    seen = []
+    for it in range(10):
+        if it == 3:     # room for one chunk's state only
+            b.client.mem_get_info = lambda dev: (per_chunk + 8 - per_chunk * b.client.n_resident, 1 << 40)
+        if it == 7:
+            b.client.mem_get_info = lambda dev: (1 << 40, 1 << 40)
+        for eng in (a, b):
+            loss = torch.nn.functional.mse_loss(eng(x).float(), y)
+            eng.backward(loss)
+            eng.step()
+        seen.append(b.client.n_resident)
+        for pa, pb in zip(a.module.parameters(), b.module.parameters()):
+            assert torch.equal(pa.data.view(torch.int16), pb.data.view(torch.int16)), it
+    assert seen == [n_local] * 3 + [1] * 4 + [n_local] * 3, seen
+    for k in range(n_local):
+        for ta, tb in zip(a.client.chunk_state(k), b.client.chunk_state(k)):
+            assert torch.equal(ta.cpu().view(torch.int32), tb.cpu().view(torch.int32)), k
+    assert a.optimizer.step_count == b.optimizer.step_count == 10
