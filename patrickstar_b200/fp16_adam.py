@@ -27,6 +27,7 @@ Differences from the reference that a user can see
     neither tested for overflow nor divided by the world size.
 """
 import ctypes as C
+import logging
 from copy import deepcopy
 
 import numpy as np
@@ -36,6 +37,9 @@ from ._lib import (CHUNK_DESC_DTYPE, PS_MAX_GROUPS, SEGMENT_DTYPE, TENSOR_DESC_D
                    StepCtrl, StepPlan, check, lib)
 from .loss_scaler import DynamicLossScaler, _DeviceScaler
 from .timers import ADAM, ADAM_COMPUTE, ADAM_OFFLOAD, ADAM_OVERFLOW_SCAN, PhaseTimer
+
+
+logger = logging.getLogger("PatrickStar")   # the reference's logger name (patrickstar/utils/logging.py:36)
 
 
 class _NoScaler(_DeviceScaler):
@@ -121,6 +125,10 @@ class FP16Adam(torch.optim.Optimizer):
 
         # section timing of the step on CUDA events (off by default; no sync either way)
         self.time_profile = False
+        # The reference logs "Gradient overflow! Update loss scale from X to Y." on a skipped step
+        # (fp16_cpu_adam.py:549-558).  Here the decision is taken on the device, so the message
+        # costs a read-back (a synchronisation) per step and is off unless asked for.
+        self.log_overflow = False
         # optional callable(name): called between the phases of the fused multi-GPU step so that
         # a benchmark can drop CUDA events there ("scan", "flag", "kernel", "barrier" = phase done)
         self.phase_marker = None
@@ -313,6 +321,7 @@ class FP16Adam(torch.optim.Optimizer):
         tp = self.time_profile
         with torch.cuda.device(self.device):
             st = self._stream()
+            old_scale = self._scaler.loss_scale if (self.log_overflow and self._dynamic) else None
             if tp:
                 self.timer.start_profile(ADAM)
             if self._dynamic:
@@ -323,6 +332,7 @@ class FP16Adam(torch.optim.Optimizer):
                                                self._scaler.flag_ptr, st), "ps_overflow_scan")
                     if tp:
                         self.timer.finish_profile(ADAM_OVERFLOW_SCAN)
+                        self.timer.update_bytes(ADAM_OVERFLOW_SCAN, 2 * int(self._desc_host["numel"][:self._n_local].sum()))
                 c.all_reduce_flag(self._scaler.flag_tensor)
             self._begin(grad_divisor, st)
             if tp:
@@ -331,6 +341,8 @@ class FP16Adam(torch.optim.Optimizer):
             self._update_torch_params(st)
             if tp:
                 self.timer.finish_profile(ADAM_COMPUTE)
+                # 28 B per updated parameter (a skipped step moves 6 B; the counter states the update's)
+                self.timer.update_bytes(ADAM_COMPUTE, 28 * int(self._desc_host["numel"][:c.n_resident].sum()))
             if self._offload is not None:
                 if tp:
                     self.timer.start_profile(ADAM_OFFLOAD)
@@ -339,6 +351,8 @@ class FP16Adam(torch.optim.Optimizer):
                     self.timer.finish_profile(ADAM_OFFLOAD)
             if tp:
                 self.timer.finish_profile(ADAM)
+            if old_scale is not None and self.read_ctrl().skip:
+                logger.warning("Gradient overflow! Update loss scale from %s to %s.", old_scale, self._scaler.loss_scale)
         return loss
 
     def _update_torch_params(self, st):

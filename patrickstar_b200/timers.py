@@ -23,6 +23,17 @@ class PhaseTimer:
     def __init__(self):
         self._open = {}
         self._pairs = OrderedDict()
+        self._bytes = OrderedDict()   # key -> bytes moved, the reference's DataMoveCnter (global_timer.py:94-126)
+
+    def update_bytes(self, key, nbytes):
+        """Account ``nbytes`` of memory traffic to a section (host-side bookkeeping only)."""
+        self._bytes[key] = self._bytes.get(key, 0) + int(nbytes)
+
+    def bandwidth(self):
+        """{key: GB/s} for the sections that were given byte counts; synchronises the device."""
+        times = self.summary()
+        return OrderedDict((k, b / (times[k][1] * 1e-3) / 1e9) for k, b in self._bytes.items()
+                           if k in times and times[k][1] > 0)
 
     def start_profile(self, key):
         e = torch.cuda.Event(enable_timing=True)
@@ -42,3 +53,4 @@ class PhaseTimer:
     def reset(self):
         self._open.clear()
         self._pairs.clear()
+        self._bytes.clear()

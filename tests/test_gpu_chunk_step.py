@@ -302,6 +302,33 @@ def test_section_timers_and_auto_placement():
     assert list(summ) == ["ADAM_overflow_scan", "ADAM_compute", "ADAM"]
     assert all(calls == 3 and ms > 0 for calls, ms in summ.values())
     assert summ["ADAM"][1] >= summ["ADAM_compute"][1]
+    # bytes per section, like the reference's DataMoveCnter: 2 B scanned and 28 B updated per parameter
+    assert opt.timer._bytes == {"ADAM_overflow_scan": 3 * 2 * 3 * cs, "ADAM_compute": 3 * 28 * 3 * cs}
+    bw = opt.timer.bandwidth()
+    assert set(bw) == {"ADAM_overflow_scan", "ADAM_compute"} and all(v > 0 for v in bw.values())
+
+
+def test_overflow_is_logged_on_request(caplog):
+    """fp16_cpu_adam.py:549-558: "Gradient overflow! Update loss scale from X to Y." on a skipped
+    step, under the reference's logger name; off by default because it costs a read-back."""
+    import logging
+    from patrickstar_b200 import DynamicLossScaler, FP16Adam
+    cs = 4096
+    client = make_client([("w", cs, 0)], cs)
+    opt = FP16Adam(client, client.params.values(), loss_scaler=DynamicLossScaler(init_scale=64, scale_factor=2), lr=1e-3)
+    g = torch.zeros(cs, dtype=torch.float16)
+    g[11] = float("inf")
+    with caplog.at_level(logging.WARNING, logger="PatrickStar"):
+        client.fp16_chunk(0).copy_(g)
+        opt.step()                      # silent by default
+        assert not caplog.records
+        opt.log_overflow = True
+        client.fp16_chunk(0).copy_(g)
+        opt.step()
+        client.fp16_chunk(0).zero_()
+        opt.step()                      # a clean step logs nothing
+    assert [r.getMessage() for r in caplog.records] == ["Gradient overflow! Update loss scale from 32 to 16."]
+    assert opt.skipped_steps == 2 and opt.step_count == 1
 
 
 def test_device_error_word_when_pow_table_is_short():
